@@ -1,0 +1,105 @@
+/*
+ * C ABI of liblightning_b200.so: Lightning Attention-2 forward/backward and SimpleRMSNorm
+ * forward/backward for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *  - Every pointer is a CUDA device pointer owned by the caller unless stated otherwise; the
+ *    library never allocates or frees device memory.
+ *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and the calls return
+ *    without synchronising (except lab200_read_status).
+ *  - Return value 0 means the work was enqueued; any other value is an error code
+ *    (lab200_error_string) and nothing was enqueued.
+ *  - Tensors are contiguous row-major. q, k: (b, h, n, d); v, o: (b, h, n, e).
+ *    `slopes` holds h fp32 decay rates (one per head, shared by the batch) or is NULL for no decay.
+ *  - dtype codes: LAB200_F32, LAB200_F16, LAB200_BF16. Attention supports F16 and BF16 with
+ *    d, e multiples of 16, d <= 256; SRMSNorm supports all three.
+ *
+ * The entry points replace the device side of the reference's torch.autograd.Functions; the
+ * reference file:line each one stands in for is given beside it (paths inside
+ * OpenNLPLab/lightning-attention).
+ */
+#ifndef LIGHTNING_B200_H_
+#define LIGHTNING_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LAB200_F32 0
+#define LAB200_F16 1
+#define LAB200_BF16 2
+
+#define LAB200_OK 0
+#define LAB200_ERR_SHAPE 1       /* unsupported or inconsistent sizes */
+#define LAB200_ERR_DTYPE 2       /* unsupported dtype code */
+#define LAB200_ERR_WORKSPACE 3   /* workspace missing or too small */
+#define LAB200_ERR_CUDA 4        /* a CUDA runtime call or launch failed */
+#define LAB200_ERR_DRIVER 5      /* the driver lacks cuTensorMapEncodeTiled or refused the tensor map */
+#define LAB200_ERR_ALIGN 6       /* a pointer is not 16-byte aligned */
+#define LAB200_ERR_WAIT_INPUT 101 /* device side: a bounded barrier wait ran out (see lab200_read_status) */
+#define LAB200_ERR_WAIT_MMA1 102
+#define LAB200_ERR_WAIT_MMA2 103
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+int lab200_version(void);
+
+/* Static, human-readable text for an error code. */
+const char* lab200_error_string(int code);
+
+/* Number of sequence chunks the library would pick for this problem on the current device when
+ * `chunks` = 0 is passed to the calls below (1 = one serial sweep per (batch, head)). */
+int lab200_la_plan_chunks(int bh, int n, int dk, int dv);
+
+/* Bytes of workspace the attention calls below need for the given sizes; `chunks` as passed to
+ * the call (0 = automatic). Always at least 256 (a status block lives in front). */
+size_t lab200_la_workspace_bytes(int bh, int n, int dk, int dv, int chunks);
+
+/*
+ * The generic decayed causal product that all four attention results are instances of:
+ *   reverse = 0:  out_t = sum_{j<=t} lambda^(t-j) (a_t . bm_j) c_j
+ *   reverse = 1:  out_t = sum_{j>=t} lambda^(j-t) (a_t . bm_j) c_j
+ * a, bm: (bh, n, dk); c, out: (bh, n, dv); lambda = exp(-slopes[bh % h]).
+ * state_in / state_out: optional (bh, dv, dk) fp32 running state entering / leaving the sequence
+ * (the transposed d x e "KV" matrix of lightning_attn2.py:55,84), for sequence-parallel chaining;
+ * chaining requires n to be a multiple of 128.
+ * state_only != 0 computes only state_out (a, out may be NULL).
+ * chunks: 0 = automatic, otherwise the number of sequence chunks processed by independent CTAs.
+ * Stands in for _fwd_kernel (lightning_attn2.py:8-85), _bwd_intra_kernel (:88-183) and
+ * _bwd_inter_kernel (:186-395), which are the four role assignments of this product.
+ */
+int lab200_la_generic(const void* a, const void* bm, const void* c, const float* slopes, void* out,
+                      const float* state_in, float* state_out, void* workspace, size_t workspace_bytes,
+                      int bh, int h, int n, int dk, int dv, int reverse, int state_only, int chunks,
+                      int dtype, void* stream);
+
+/* o = LightningAttention2.forward(q, k, v, s): lightning_attn2.py:400-434 (with slopes) and
+ * lightning_attn2_no_decay.py:368-400 (slopes = NULL). */
+int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slopes, void* o,
+                   void* workspace, size_t workspace_bytes, int b, int h, int n, int d, int e,
+                   int chunks, int dtype, void* stream);
+
+/* dq, dk, dv = LightningAttention2.backward(do): lightning_attn2.py:437-504 and
+ * lightning_attn2_no_decay.py:403-468. Workspace size: lab200_la_workspace_bytes(b*h, n, max(d,e), max(d,e), chunks). */
+int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slopes, const void* dout,
+                   void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h,
+                   int n, int d, int e, int chunks, int dtype, void* stream);
+
+/* Synchronises `stream` and returns the device-side status word of the last attention call that
+ * used `workspace` (0, or one of LAB200_ERR_WAIT_*). Negative: the copy itself failed. */
+int lab200_read_status(const void* workspace, void* stream);
+
+/* y = x * rsqrt(mean(x^2, last dim) + eps), rstd saved per row: _SrmsNorm.forward /
+ * srms_norm_fw, srmsnorm.py:12-33, 78-122. x, y: (M, N); rstd: (M) fp32. N * sizeof(elem) <= 65536. */
+int lab200_srmsnorm_fwd(const void* x, void* y, float* rstd, long long M, int N, float eps, int dtype,
+                        void* stream);
+
+/* dx for the above: _SrmsNorm.backward / srms_norm_bwd_dx_fused, srmsnorm.py:38-74, 125-175. */
+int lab200_srmsnorm_bwd(const void* x, const void* dy, const float* rstd, void* dx, long long M, int N,
+                        int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIGHTNING_B200_H_ */

@@ -1,0 +1,59 @@
+"""Builds liblightning_b200.so (the C-ABI library with all sm_100a kernels) in-tree with nvcc.
+
+Run as ``python -m lightning_attention_b200.build``. Cross-compiles without a GPU.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_NAME = "liblightning_b200.so"
+LIB_PATH = os.path.join(HERE, LIB_NAME)
+SOURCES = [os.path.join(HERE, "csrc", "capi.cu")]
+HEADERS = [
+    os.path.join(HERE, "csrc", "ptx_sm100.cuh"),
+    os.path.join(HERE, "csrc", "la_kernels.cuh"),
+    os.path.join(HERE, "csrc", "srmsnorm_kernels.cuh"),
+    os.path.join(HERE, "..", "include", "lightning_b200.h"),
+]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+
+
+def find_nvcc():
+    nvcc = shutil.which("nvcc")
+    if nvcc is None:
+        cand = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+        if os.path.exists(cand):
+            nvcc = cand
+    if nvcc is None:
+        raise RuntimeError("nvcc not found; cannot build " + LIB_NAME)
+    return nvcc
+
+
+def up_to_date():
+    if not os.path.exists(LIB_PATH):
+        return False
+    t = os.path.getmtime(LIB_PATH)
+    return all(os.path.getmtime(f) <= t for f in SOURCES + HEADERS if os.path.exists(f))
+
+
+def build(force=False, verbose=False):
+    """Compile the library if it is missing or older than its sources. Returns its path."""
+    if not force and up_to_date():
+        return LIB_PATH
+    cmd = [find_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + SOURCES
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,395 @@
+// C-ABI entry points of liblightning_b200.so (declared in include/lightning_b200.h).
+// Host side only: argument checks, tensor-map encoding, kernel selection and launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <mutex>
+
+#include "../../include/lightning_b200.h"
+#include "la_kernels.cuh"
+#include "srmsnorm_kernels.cuh"
+
+using namespace lab200;
+
+namespace {
+
+constexpr size_t WS_HEADER = 256;            // status block in front of the workspace
+constexpr int SMEM_LIMIT = 232448;           // 227 KB opt-in dynamic shared memory per CTA
+constexpr long long WAIT_BUDGET = 2000000000LL;  // ~1 s of SM clocks per barrier wait
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+int sm_count() {
+  int dev = 0, n = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n > 0 ? n : 148;
+}
+
+// (bh, n, dim) row-major 16-bit tensor -> boxes of 64 features x 128 tokens, 128-byte swizzle,
+// out-of-range rows and columns read as zero.
+int make_tmap(CUtensorMap* tm, const void* ptr, int bh, int n, int dim, int dtype) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return LAB200_ERR_DRIVER;
+  const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(dim), static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(bh)};
+  const cuuint64_t gstr[2] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(n) * dim * 2};
+  const cuuint32_t box[3] = {64, LA_BLOCK, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = (dtype == LAB200_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(tm, dt, 3, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LAB200_OK : LAB200_ERR_DRIVER;
+}
+
+struct Tiling {
+  int nks, nvs, nslices, nstage_full;
+};
+
+bool pick_tiling(int dk, int dv, Tiling* t) {
+  if (dk < 16 || dv < 16 || (dk % 16) || (dv % 16) || dk > 256) return false;
+  t->nks = (dk + 63) / 64;
+  t->nvs = (t->nks <= 2 && dv > 64) ? 2 : 1;
+  t->nslices = (dv + 64 * t->nvs - 1) / (64 * t->nvs);
+  if (t->nslices > 65535) return false;
+  return true;
+}
+
+int smem_bytes(int nks, int nvs, int mode, int nstage) {
+  const int slab = LA_SLAB_BYTES;
+  int b = nstage * (nks + 2) * slab;
+  if (mode == 0) b += nks * slab + 2 * slab + nks * nvs * 64 * 128;
+  return b + 64 + 1024;  // barriers + alignment slack
+}
+
+int plan_chunks(int bh, int n, int dk, int dv) {
+  Tiling t;
+  if (!pick_tiling(dk, dv, &t)) return 1;
+  const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
+  const long long units = static_cast<long long>(bh) * t.nslices;
+  const int sms = sm_count();
+  if (units * 10 >= sms * 8LL) return 1;  // a serial sweep per unit already fills >= 80 % of the SMs
+  long long c = sms / (units > 0 ? units : 1);
+  const int max_c = nblocks / 2 > 0 ? nblocks / 2 : 1;  // at least two blocks per chunk
+  if (c > max_c) c = max_c;
+  if (c < 1) c = 1;
+  return static_cast<int>(c);
+}
+
+template <int NKS, int NVS, int MODE, int FMT>
+int launch_one(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const LaParams& p, dim3 grid,
+               int smem, cudaStream_t st) {
+  auto kern = la_chunk_kernel<NKS, NVS, MODE, FMT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return LAB200_ERR_CUDA;
+  }
+  kern<<<grid, LA_THREADS, smem, st>>>(tA, tB, tC, p);
+  return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
+}
+
+template <int MODE, int FMT>
+int launch_tiled(int nks, int nvs, const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
+                 const LaParams& p, dim3 grid, int smem, cudaStream_t st) {
+#define LAB200_CASE(K, V) \
+  if (nks == K && nvs == V) return launch_one<K, V, MODE, FMT>(tA, tB, tC, p, grid, smem, st);
+  LAB200_CASE(1, 1)
+  LAB200_CASE(1, 2)
+  LAB200_CASE(2, 1)
+  LAB200_CASE(2, 2)
+  LAB200_CASE(3, 1)
+  LAB200_CASE(4, 1)
+#undef LAB200_CASE
+  return LAB200_ERR_SHAPE;
+}
+
+int launch_la(int mode, int dtype, const Tiling& t, const CUtensorMap& tA, const CUtensorMap& tB,
+              const CUtensorMap& tC, LaParams p, int nchunks_grid, int bh, cudaStream_t st) {
+  int nstage = 2;
+  int smem = smem_bytes(t.nks, t.nvs, mode, nstage);
+  if (smem > SMEM_LIMIT) {
+    nstage = 1;
+    smem = smem_bytes(t.nks, t.nvs, mode, nstage);
+  }
+  if (smem > SMEM_LIMIT) return LAB200_ERR_SHAPE;
+  p.nstage = nstage;
+  const dim3 grid(t.nslices, nchunks_grid, bh);
+  if (mode == 0) {
+    return dtype == LAB200_BF16 ? launch_tiled<0, 1>(t.nks, t.nvs, tA, tB, tC, p, grid, smem, st)
+                                : launch_tiled<0, 0>(t.nks, t.nvs, tA, tB, tC, p, grid, smem, st);
+  }
+  return dtype == LAB200_BF16 ? launch_tiled<1, 1>(t.nks, t.nvs, tA, tB, tC, p, grid, smem, st)
+                              : launch_tiled<1, 0>(t.nks, t.nvs, tA, tB, tC, p, grid, smem, st);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int la_validate(const void* a, const void* bm, const void* c, const void* out, const float* state_in,
+                const float* state_out, const void* workspace, int bh, int h, int n, int dk, int dv, int state_only,
+                int dtype);
+
+// The generic product without the status reset (so that composite calls share one status word).
+int la_generic_impl(const void* a, const void* bm, const void* c, const float* slopes, void* out,
+                    const float* state_in, float* state_out, void* workspace, size_t workspace_bytes, int bh, int h,
+                    int n, int dk, int dv, int reverse, int state_only, int chunks, int dtype, cudaStream_t st) {
+  int rc = la_validate(a, bm, c, out, state_in, state_out, workspace, bh, h, n, dk, dv, state_only, dtype);
+  if (rc != LAB200_OK) return rc;
+  Tiling t;
+  pick_tiling(dk, dv, &t);
+  const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
+  int nchunks = chunks > 0 ? chunks : plan_chunks(bh, n, dk, dv);
+  if (nchunks > nblocks) nchunks = nblocks;
+  const int bpc = (nblocks + nchunks - 1) / nchunks;
+  nchunks = (nblocks + bpc - 1) / bpc;  // drop empty trailing chunks
+  if (nchunks > 65535) return LAB200_ERR_SHAPE;
+  const size_t need = WS_HEADER + (nchunks > 1 ? static_cast<size_t>(bh) * nchunks * dv * dk * sizeof(float) : 0);
+  if (!workspace || workspace_bytes < need) return LAB200_ERR_WORKSPACE;
+
+  CUtensorMap tA, tB, tC;
+  if ((rc = make_tmap(&tB, bm, bh, n, dk, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tC, c, bh, n, dv, dtype)) != LAB200_OK) return rc;
+  if (state_only) {
+    tA = tB;
+  } else if ((rc = make_tmap(&tA, a, bh, n, dk, dtype)) != LAB200_OK) {
+    return rc;
+  }
+
+  LaParams p;
+  p.out = out;
+  p.slopes = slopes;
+  p.status = static_cast<int*>(workspace);
+  p.n = n; p.h = h; p.dk = dk; p.dv = dv;
+  p.nblocks = nblocks;
+  p.blocks_per_chunk = bpc;
+  p.reverse = reverse ? 1 : 0;
+  p.nstage = 2;
+  p.wait_budget = WAIT_BUDGET;
+
+  if (nchunks == 1) {
+    p.chunk0 = 0;
+    p.state_slots = 1;
+    p.state_in = state_in;
+    p.state_out = state_out;
+    return launch_la(state_only ? 1 : 0, dtype, t, tA, tB, tC, p, 1, bh, st);
+  }
+
+  // three phases: local chunk states -> decayed scan -> block loop per chunk with its incoming state
+  float* states = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + WS_HEADER);
+  const bool need_total = (state_out != nullptr);
+  const int skip_last = need_total ? 0 : 1;
+  p.state_slots = nchunks;
+  p.state_in = nullptr;
+  p.state_out = states;
+  p.chunk0 = (skip_last && reverse) ? 1 : 0;
+  if ((rc = launch_la(1, dtype, t, tB, tB, tC, p, nchunks - skip_last, bh, st)) != LAB200_OK) return rc;
+
+  const int elems = dv * dk;
+  const long long total = static_cast<long long>(bh) * elems;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  la_scan_kernel<<<blocks, threads, 0, st>>>(states, state_in, state_out, slopes, h, nchunks, elems, nblocks, bpc,
+                                             p.reverse, skip_last, total);
+  if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
+  if (state_only) return LAB200_OK;
+
+  p.chunk0 = 0;
+  p.state_in = states;
+  p.state_out = nullptr;
+  return launch_la(0, dtype, t, tA, tB, tC, p, nchunks, bh, st);
+}
+
+// Argument checks that need no CUDA call; run before anything is enqueued.
+int la_validate(const void* a, const void* bm, const void* c, const void* out, const float* state_in,
+                const float* state_out, const void* workspace, int bh, int h, int n, int dk, int dv, int state_only,
+                int dtype) {
+  if (dtype != LAB200_BF16 && dtype != LAB200_F16) return LAB200_ERR_DTYPE;
+  Tiling t;
+  if (bh < 1 || bh > 65535 || h < 1 || n < 1 || !pick_tiling(dk, dv, &t)) return LAB200_ERR_SHAPE;
+  if (!bm || !c || (!state_only && (!a || !out)) || (state_only && !state_out)) return LAB200_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(bm) || !aligned16(c) || !aligned16(out) || !aligned16(state_in) ||
+      !aligned16(state_out) || !aligned16(workspace))
+    return LAB200_ERR_ALIGN;
+  return LAB200_OK;
+}
+
+int reset_status(void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!workspace || workspace_bytes < WS_HEADER) return LAB200_ERR_WORKSPACE;
+  return cudaMemsetAsync(workspace, 0, 16, st) == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SRMSNorm launch selection
+// ---------------------------------------------------------------------------------------------
+template <int DT, int G, int VPT>
+void srms_launch(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
+                 cudaStream_t st) {
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  const unsigned grid = static_cast<unsigned>((M + RPC - 1) / RPC);
+  if (fwd) {
+    srmsnorm_fwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, out, rstd, static_cast<int>(M), N, eps);
+  } else {
+    srmsnorm_bwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, dy, rstd, out, static_cast<int>(M), N);
+  }
+}
+
+template <int DT>
+int srms_dispatch(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
+                  cudaStream_t st) {
+  constexpr int EPV = SrmsVec<DT>::EPV;
+  const bool vec_ok = (N % EPV == 0) && aligned16(x) && aligned16(out) && (fwd || aligned16(dy));
+  if (!vec_ok) {
+    const unsigned grid = static_cast<unsigned>(M);
+    if (fwd) {
+      srmsnorm_fwd_generic_kernel<DT><<<grid, 256, 0, st>>>(x, out, rstd, static_cast<int>(M), N, eps);
+    } else {
+      srmsnorm_bwd_generic_kernel<DT><<<grid, 256, 0, st>>>(x, dy, rstd, out, static_cast<int>(M), N);
+    }
+    return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
+  }
+  const int nvec = N / EPV;
+  // smallest G * VPT that covers the row; among equals the one with fewer threads per row
+#define LAB200_SRMS(G, V) \
+  if (nvec <= G * V) { srms_launch<DT, G, V>(fwd, x, dy, out, rstd, M, N, eps, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
+  LAB200_SRMS(32, 2)
+  LAB200_SRMS(32, 4)
+  LAB200_SRMS(32, 8)
+  LAB200_SRMS(128, 4)
+  LAB200_SRMS(128, 8)
+  LAB200_SRMS(256, 8)
+  LAB200_SRMS(512, 8)
+#undef LAB200_SRMS
+  return LAB200_ERR_SHAPE;
+}
+
+int srms_entry(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
+               int dtype, cudaStream_t st) {
+  if (M < 0 || N < 1 || M > 2147483647LL) return LAB200_ERR_SHAPE;
+  if (!x || !out || !rstd || (!fwd && !dy)) return M == 0 ? LAB200_OK : LAB200_ERR_SHAPE;
+  if (M == 0) return LAB200_OK;
+  const int esz = (dtype == LAB200_F32) ? 4 : 2;
+  if (static_cast<long long>(N) * esz > 65536) return LAB200_ERR_SHAPE;  // same limit as srmsnorm.py:94-97
+  switch (dtype) {
+    case LAB200_F32: return srms_dispatch<SRMS_F32>(fwd, x, dy, out, rstd, M, N, eps, st);
+    case LAB200_F16: return srms_dispatch<SRMS_F16>(fwd, x, dy, out, rstd, M, N, eps, st);
+    case LAB200_BF16: return srms_dispatch<SRMS_BF16>(fwd, x, dy, out, rstd, M, N, eps, st);
+    default: return LAB200_ERR_DTYPE;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int lab200_version(void) { return 100; }
+
+const char* lab200_error_string(int code) {
+  switch (code) {
+    case LAB200_OK: return "ok";
+    case LAB200_ERR_SHAPE: return "unsupported or inconsistent sizes";
+    case LAB200_ERR_DTYPE: return "unsupported dtype";
+    case LAB200_ERR_WORKSPACE: return "workspace missing or too small";
+    case LAB200_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+    case LAB200_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or refused the tensor map";
+    case LAB200_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case LAB200_ERR_WAIT_INPUT: return "device: bounded wait for TMA input ran out";
+    case LAB200_ERR_WAIT_MMA1: return "device: bounded wait for the first MMA group ran out";
+    case LAB200_ERR_WAIT_MMA2: return "device: bounded wait for the second MMA group ran out";
+    default: return "unknown error";
+  }
+}
+
+int lab200_la_plan_chunks(int bh, int n, int dk, int dv) { return plan_chunks(bh, n, dk, dv); }
+
+size_t lab200_la_workspace_bytes(int bh, int n, int dk, int dv, int chunks) {
+  if (bh < 1 || n < 1 || dk < 1 || dv < 1) return WS_HEADER;
+  const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
+  int nchunks = chunks > 0 ? chunks : plan_chunks(bh, n, dk, dv);
+  if (nchunks > nblocks) nchunks = nblocks;
+  if (nchunks <= 1) return WS_HEADER;
+  return WS_HEADER + static_cast<size_t>(bh) * nchunks * dv * dk * sizeof(float);
+}
+
+int lab200_la_generic(const void* a, const void* bm, const void* c, const float* slopes, void* out,
+                      const float* state_in, float* state_out, void* workspace, size_t workspace_bytes, int bh,
+                      int h, int n, int dk, int dv, int reverse, int state_only, int chunks, int dtype,
+                      void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = la_validate(a, bm, c, out, state_in, state_out, workspace, bh, h, n, dk, dv, state_only, dtype);
+  if (rc != LAB200_OK) return rc;
+  if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
+  return la_generic_impl(a, bm, c, slopes, out, state_in, state_out, workspace, workspace_bytes, bh, h, n, dk, dv,
+                         reverse, state_only, chunks, dtype, st);
+}
+
+int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slopes, void* o, void* workspace,
+                   size_t workspace_bytes, int b, int h, int n, int d, int e, int chunks, int dtype, void* stream) {
+  if (b < 1 || h < 1 || b > 65535 / h) return LAB200_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = la_validate(q, k, v, o, nullptr, nullptr, workspace, b * h, h, n, d, e, 0, dtype);
+  if (rc != LAB200_OK) return rc;
+  if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
+  return la_generic_impl(q, k, v, slopes, o, nullptr, nullptr, workspace, workspace_bytes, b * h, h, n, d, e, 0, 0,
+                         chunks, dtype, st);
+}
+
+int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dq,
+                   void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h, int n, int d, int e,
+                   int chunks, int dtype, void* stream) {
+  if (b < 1 || h < 1 || b > 65535 / h) return LAB200_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int bh = b * h;
+  int rc = la_validate(dout, v, k, dq, nullptr, nullptr, workspace, bh, h, n, e, d, 0, dtype);
+  if (rc == LAB200_OK) rc = la_validate(k, q, dout, dv, nullptr, nullptr, workspace, bh, h, n, d, e, 0, dtype);
+  if (rc == LAB200_OK && (!q || !dk || !aligned16(q) || !aligned16(dk))) rc = q && dk ? LAB200_ERR_ALIGN : LAB200_ERR_SHAPE;
+  if (rc != LAB200_OK) return rc;
+  if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
+  // dq_t = sum_{j<=t} lambda^(t-j) (do_t . v_j) k_j
+  rc = la_generic_impl(dout, v, k, slopes, dq, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, e, d, 0, 0,
+                       chunks, dtype, st);
+  if (rc != LAB200_OK) return rc;
+  // dk_t = sum_{j>=t} lambda^(j-t) (v_t . do_j) q_j
+  rc = la_generic_impl(v, dout, q, slopes, dk, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, e, d, 1, 0,
+                       chunks, dtype, st);
+  if (rc != LAB200_OK) return rc;
+  // dv_t = sum_{j>=t} lambda^(j-t) (k_t . q_j) do_j
+  return la_generic_impl(k, q, dout, slopes, dv, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, d, e, 1, 0,
+                         chunks, dtype, st);
+}
+
+int lab200_read_status(const void* workspace, void* stream) {
+  if (!workspace) return -1;
+  int v = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&v, workspace, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -2;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return -3;
+  return v;
+}
+
+int lab200_srmsnorm_fwd(const void* x, void* y, float* rstd, long long M, int N, float eps, int dtype, void* stream) {
+  return srms_entry(true, x, nullptr, y, rstd, M, N, eps, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int lab200_srmsnorm_bwd(const void* x, const void* dy, const float* rstd, void* dx, long long M, int N, int dtype,
+                        void* stream) {
+  return srms_entry(false, x, dy, dx, const_cast<float*>(rstd), M, N, 0.f, dtype, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

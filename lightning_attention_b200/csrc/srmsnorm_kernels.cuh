@@ -1,0 +1,239 @@
+// SimpleRMSNorm (no learnable weight) forward and backward for sm_100a.
+//
+//   forward : rstd = 1 / sqrt(mean(x^2) + eps);  y = x * rstd            (reference: srmsnorm.py:12-33)
+//   backward: xhat = x * rstd; c = mean(xhat * dy); dx = (dy - xhat * c) * rstd   (srmsnorm.py:38-74)
+//
+// Both are pure streaming kernels (4 and 6 bytes per bf16 element). A row is owned by a group of G
+// threads; every thread keeps its part of the row in registers as 128-bit vectors, so each element
+// is read from HBM exactly once. Sums are fp32: warp shuffles first, then (G > 32) a few words of
+// shared memory.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lab200 {
+
+constexpr int SRMS_MAX_VPT = 8;  // most 128-bit vectors a thread may hold
+
+enum SrmsDtype : int { SRMS_F32 = 0, SRMS_F16 = 1, SRMS_BF16 = 2 };
+
+template <int DT> struct SrmsVec;
+template <> struct SrmsVec<SRMS_F32> {
+  static constexpr int EPV = 4;
+  __device__ static void unpack(const uint4& u, float* f) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+  __device__ static uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+template <> struct SrmsVec<SRMS_F16> {
+  static constexpr int EPV = 8;
+  __device__ static void unpack(const uint4& u, float* f) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ static uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct SrmsVec<SRMS_BF16> {
+  static constexpr int EPV = 8;
+  __device__ static void unpack(const uint4& u, float* f) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ static uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(uint4* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Sum over the G threads that own one row. `slot` is this row group's scratch in shared memory.
+template <int G>
+__device__ __forceinline__ float group_sum(float v, float* slot, int tig) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if constexpr (G > 32) {
+    constexpr int NW = G / 32;
+    if ((tig & 31) == 0) slot[tig >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) t += slot[w];
+    __syncthreads();  // slot is reused by the next reduction
+    v = t;
+  }
+  return v;
+}
+
+// G threads per row holding VPT vectors each; CTA = max(G, 256) threads => CTA / G rows per CTA.
+template <int DT, int G, int VPT>
+__global__ void __launch_bounds__((G > 256 ? G : 256))
+srmsnorm_fwd_kernel(const void* __restrict__ x_, void* __restrict__ y_, float* __restrict__ rstd_, int M, int N, float eps) {
+  using V = SrmsVec<DT>;
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  __shared__ float red[RPC][16];
+  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
+  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
+  const bool active = row < M;  // whole groups are (in)active together; inactive ones still reach the barriers
+  const int nvec = N / V::EPV;
+  const uint4* x = reinterpret_cast<const uint4*>(x_) + (active ? row : 0) * nvec;
+  uint4* y = reinterpret_cast<uint4*>(y_) + (active ? row : 0) * nvec;
+
+  uint4 xv[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      xv[i] = ld_stream(x + v);
+      float f[V::EPV];
+      V::unpack(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+  }
+  ss = group_sum<G>(ss, red[grp], tig);
+  const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
+  if (active && tig == 0) rstd_[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      float f[V::EPV];
+      V::unpack(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) f[j] *= rstd;
+      st_stream(y + v, V::pack(f));
+    }
+  }
+}
+
+template <int DT, int G, int VPT>
+__global__ void __launch_bounds__((G > 256 ? G : 256))
+srmsnorm_bwd_kernel(const void* __restrict__ x_, const void* __restrict__ dy_, const float* __restrict__ rstd_,
+                    void* __restrict__ dx_, int M, int N) {
+  using V = SrmsVec<DT>;
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  __shared__ float red[RPC][16];
+  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
+  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
+  const bool active = row < M;
+  const int nvec = N / V::EPV;
+  const size_t off = static_cast<size_t>(active ? row : 0) * nvec;
+  const uint4* x = reinterpret_cast<const uint4*>(x_) + off;
+  const uint4* dy = reinterpret_cast<const uint4*>(dy_) + off;
+  uint4* dx = reinterpret_cast<uint4*>(dx_) + off;
+  const float rstd = active ? rstd_[row] : 0.f;
+
+  uint4 xv[VPT], gv[VPT];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      xv[i] = ld_stream(x + v);
+      gv[i] = ld_stream(dy + v);
+      float fx[V::EPV], fg[V::EPV];
+      V::unpack(xv[i], fx);
+      V::unpack(gv[i], fg);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fg[j], dot);
+    }
+  }
+  dot = group_sum<G>(dot, red[grp], tig);
+  const float c = dot / static_cast<float>(N);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      float fx[V::EPV], fg[V::EPV];
+      V::unpack(xv[i], fx);
+      V::unpack(gv[i], fg);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
+      st_stream(dx + v, V::pack(fg));
+    }
+  }
+}
+
+// Fallback for rows whose length or base address does not allow 128-bit vectors: one 256-thread
+// CTA per row, element-wise loads, the row is read twice (the second read normally hits L2).
+template <int DT> struct SrmsElem;
+template <> struct SrmsElem<SRMS_F32> { using T = float;
+  __device__ static float ld(const T* p) { return *p; } __device__ static void st(T* p, float v) { *p = v; } };
+template <> struct SrmsElem<SRMS_F16> { using T = __half;
+  __device__ static float ld(const T* p) { return __half2float(*p); } __device__ static void st(T* p, float v) { *p = __float2half_rn(v); } };
+template <> struct SrmsElem<SRMS_BF16> { using T = __nv_bfloat16;
+  __device__ static float ld(const T* p) { return __bfloat162float(*p); } __device__ static void st(T* p, float v) { *p = __float2bfloat16_rn(v); } };
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+srmsnorm_fwd_generic_kernel(const void* __restrict__ x_, void* __restrict__ y_, float* __restrict__ rstd_, int M, int N, float eps) {
+  using E = SrmsElem<DT>;
+  __shared__ float red[1][16];
+  const size_t off = static_cast<size_t>(blockIdx.x) * N;
+  const typename E::T* x = static_cast<const typename E::T*>(x_) + off;
+  typename E::T* y = static_cast<typename E::T*>(y_) + off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < N; i += 256) { const float f = E::ld(x + i); ss = fmaf(f, f, ss); }
+  ss = group_sum<256>(ss, red[0], threadIdx.x);
+  const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
+  if (threadIdx.x == 0) rstd_[blockIdx.x] = rstd;
+  for (int i = threadIdx.x; i < N; i += 256) E::st(y + i, E::ld(x + i) * rstd);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+srmsnorm_bwd_generic_kernel(const void* __restrict__ x_, const void* __restrict__ dy_, const float* __restrict__ rstd_,
+                            void* __restrict__ dx_, int M, int N) {
+  using E = SrmsElem<DT>;
+  __shared__ float red[1][16];
+  const size_t off = static_cast<size_t>(blockIdx.x) * N;
+  const typename E::T* x = static_cast<const typename E::T*>(x_) + off;
+  const typename E::T* dy = static_cast<const typename E::T*>(dy_) + off;
+  typename E::T* dx = static_cast<typename E::T*>(dx_) + off;
+  const float rstd = rstd_[blockIdx.x];
+  float dot = 0.f;
+  for (int i = threadIdx.x; i < N; i += 256) dot = fmaf(E::ld(x + i) * rstd, E::ld(dy + i), dot);
+  dot = group_sum<256>(dot, red[0], threadIdx.x);
+  const float c = dot / static_cast<float>(N);
+  for (int i = threadIdx.x; i < N; i += 256) E::st(dx + i, (E::ld(dy + i) - E::ld(x + i) * rstd * c) * rstd);
+}
+
+}  // namespace lab200

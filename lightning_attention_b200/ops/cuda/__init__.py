@@ -1,0 +1,9 @@
+from .lightning_attn2 import (  # noqa: F401
+    LightningAttention2,
+    LightningAttention2NoDecay,
+    lightning_attn2,
+    lightning_attn2_no_decay,
+    lightning_attn2_parallel,
+    la_generic,
+)
+from .srmsnorm import SimpleRMSNorm, _SrmsNorm  # noqa: F401

@@ -1,0 +1,150 @@
+"""torch.autograd.Functions for Lightning Attention-2 backed by liblightning_b200.so.
+
+Mirrors the operator layer of the reference: ``LightningAttention2`` / ``lightning_attn2``
+(lightning_attn/ops/triton/lightning_attn2.py:398-507) and ``LightningAttention2NoDecay`` /
+``lightning_attn2_no_decay`` (lightning_attn2_no_decay.py:367-471). Inputs are made contiguous,
+outputs are allocated here with torch, (q, k, v, s) are saved for backward, and ``s`` receives no
+gradient, exactly as there. All device work goes through the C ABI on the current CUDA stream.
+"""
+import torch
+
+from ... import _lib
+
+
+def _slopes_arg(s, h, device):
+    """First h entries of `s` as contiguous fp32 on `device` (the reference kernels read S + head index,
+    lightning_attn2.py:26,39-42), or None."""
+    if s is None:
+        return None
+    flat = s.detach().to(device=device, dtype=torch.float32).contiguous().view(-1)
+    if flat.numel() < h:
+        raise RuntimeError(f"slope tensor has {flat.numel()} entries, need at least h={h}")
+    return flat[:h].contiguous()
+
+
+def _workspace(nbytes, device):
+    return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+
+def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0):
+    """The decayed causal product all attention results are instances of (see include/lightning_b200.h).
+
+    a, bm: (b, h, n, dk); c: (b, h, n, dv). Returns (out, state_out) with out (b, h, n, dv) in the
+    input dtype (None when state_only) and state_out (b, h, dv, dk) fp32 (None unless requested).
+    state_in, if given, has the shape of state_out and is the running state entering the sequence.
+    """
+    _lib.require_cuda(a, bm, c)
+    b, h, n, dk = bm.shape
+    dv = c.shape[-1]
+    dev = bm.device
+    bm = bm.contiguous()
+    c = c.contiguous()
+    a = None if state_only else a.contiguous()
+    sl = _slopes_arg(s, h, dev)
+    out = None if state_only else torch.empty((b, h, n, dv), dtype=bm.dtype, device=dev)
+    if state_in is not None:
+        state_in = state_in.to(device=dev, dtype=torch.float32).contiguous()
+        if tuple(state_in.shape) != (b, h, dv, dk):
+            raise RuntimeError(f"state_in must have shape {(b, h, dv, dk)}, got {tuple(state_in.shape)}")
+    state_out = torch.empty((b, h, dv, dk), dtype=torch.float32, device=dev) if (want_state or state_only) else None
+    L = _lib.lib()
+    nbytes = L.lab200_la_workspace_bytes(b * h, n, dk, dv, chunks)
+    ws = _workspace(nbytes, dev)
+    with torch.cuda.device(dev):
+        rc = L.lab200_la_generic(
+            _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in),
+            _lib.ptr(state_out), ws.data_ptr(), nbytes, b * h, h, n, dk, dv, int(bool(reverse)),
+            int(bool(state_only)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
+    _lib.check(rc, "lab200_la_generic")
+    return out, state_out
+
+
+def _fwd(q, k, v, sl, chunks=0):
+    b, h, n, d = q.shape
+    e = v.shape[-1]
+    o = torch.empty((b, h, n, e), dtype=q.dtype, device=q.device)
+    L = _lib.lib()
+    nbytes = L.lab200_la_workspace_bytes(b * h, n, d, e, chunks)
+    ws = _workspace(nbytes, q.device)
+    with torch.cuda.device(q.device):
+        rc = L.lab200_la2_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), o.data_ptr(), ws.data_ptr(),
+                              nbytes, b, h, n, d, e, int(chunks), _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device))
+    _lib.check(rc, "lab200_la2_fwd")
+    return o
+
+
+def _bwd(q, k, v, sl, do, chunks=0):
+    b, h, n, d = q.shape
+    e = v.shape[-1]
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    L = _lib.lib()
+    m = max(d, e)
+    nbytes = L.lab200_la_workspace_bytes(b * h, n, m, m, chunks)
+    ws = _workspace(nbytes, q.device)
+    with torch.cuda.device(q.device):
+        rc = L.lab200_la2_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), do.data_ptr(), dq.data_ptr(),
+                              dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), nbytes, b, h, n, d, e, int(chunks),
+                              _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device))
+    _lib.check(rc, "lab200_la2_bwd")
+    return dq, dk, dv
+
+
+def _check_inputs(q, k, v):
+    _lib.require_cuda(q, k, v)
+    if q.dim() != 4 or k.shape != q.shape or v.shape[:3] != q.shape[:3]:
+        raise RuntimeError(f"expected q, k (b, h, n, d) and v (b, h, n, e); got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("q, k, v must share one dtype")
+
+
+class LightningAttention2(torch.autograd.Function):
+    """o = lightning attention with per-head decay exp(-s) (lightning_attn2.py:398-504)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, s):
+        _check_inputs(q, k, v)
+        q = q.contiguous()
+        k = k.contiguous()
+        v = v.contiguous()
+        s = s.contiguous()
+        sl = _slopes_arg(s, q.shape[1], q.device)
+        o = _fwd(q, k, v, sl)
+        ctx.save_for_backward(q, k, v, s)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, s = ctx.saved_tensors
+        do = do.contiguous()
+        sl = _slopes_arg(s, q.shape[1], q.device)
+        dq, dk, dv = _bwd(q, k, v, sl, do)
+        return dq, dk, dv, None
+
+
+class LightningAttention2NoDecay(torch.autograd.Function):
+    """The same without decay (lightning_attn2_no_decay.py:367-468)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v):
+        _check_inputs(q, k, v)
+        q = q.contiguous()
+        k = k.contiguous()
+        v = v.contiguous()
+        o = _fwd(q, k, v, None)
+        ctx.save_for_backward(q, k, v)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v = ctx.saved_tensors
+        dq, dk, dv = _bwd(q, k, v, None, do.contiguous())
+        return dq, dk, dv
+
+
+lightning_attn2 = LightningAttention2.apply
+lightning_attn2_no_decay = LightningAttention2NoDecay.apply
+# The reference's "parallel" variant (lightning_attn2_parallel.py:1072) computes the same function with a
+# different kernel decomposition; here the library picks the decomposition itself.
+lightning_attn2_parallel = LightningAttention2.apply

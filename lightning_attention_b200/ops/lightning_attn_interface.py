@@ -1,0 +1,54 @@
+"""User-facing wrapper with the reference's signature (lightning_attn/ops/lightning_attn_interface.py:16-65).
+
+The reference pads e to a power of two and splits d > 128 into 64-wide slices whose partial
+outputs it sums, because its Triton kernels need power-of-two tiles. The CUDA kernels take any
+d <= 256 and any e that are multiples of 16, so here padding only happens for sizes that are not
+multiples of 16, and splitting only for d > 256 (the product q.k is additive over feature slices).
+"""
+import math
+
+import torch.nn.functional as F
+
+from .cuda import lightning_attn2, lightning_attn2_no_decay
+
+_MAX_D = 256
+
+
+def is_support(dim):
+    """The reference's quirky support test, kept for API parity (lightning_attn_interface.py:8-9):
+    falsy exactly when dim divides 16. It is not used to gate anything here."""
+    return 16 % dim
+
+
+def next_power_of_2(n):
+    return 2 ** (int(math.ceil(math.log(n, 2))))
+
+
+def _pad_last(x, mult):
+    r = (-x.shape[-1]) % mult
+    return F.pad(x, (0, r)) if r else x
+
+
+def lightning_attn_func(q, k, v, s=None, variant="chunk_loop"):
+    """o_t = sum_{j<=t} exp(-s (t-j)) (q_t . k_j) v_j per head; s=None means no decay.
+
+    `variant` is accepted for compatibility ("chunk_loop" or "parallel"); one implementation serves both.
+    """
+    if variant not in ("chunk_loop", "parallel"):
+        raise ValueError(f"unknown variant {variant!r}")
+    e = v.shape[-1]
+    q = _pad_last(q, 16)
+    k = _pad_last(k, 16)
+    v = _pad_last(v, 16)
+    d = q.shape[-1]
+
+    def fn(q1, k1):
+        return lightning_attn2_no_decay(q1, k1, v) if s is None else lightning_attn2(q1, k1, v, s)
+
+    if d > _MAX_D:
+        o = 0
+        for start in range(0, d, _MAX_D):
+            o = o + fn(q[..., start:start + _MAX_D], k[..., start:start + _MAX_D])
+    else:
+        o = fn(q, k)
+    return o[..., :e] if o.shape[-1] != e else o
