@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Benchmark of the Lightning Attention-2 forward+backward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step"): lightning_attn2 forward + backward on b=4, h=32, n=32768, d=e=128, bf16,
+q/k/v/do ~ N(0,1) from seed 2024, ALiBi-style slopes -- the largest point of the reference's
+benchmark sweep (benchmarks/benchmark_lightning2.py:56-118). Metric: tokens/s (tokens = b*n per step).
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same workload on its own
+(batch, head) units with no communication (weak scaling); the value is the sum over ranks divided by
+the slowest rank's time.
+
+Rank 0 prints ONE JSON line. `--impl reference` times the CPU restatement of the reference's
+recurrences (oracle/) on the host cores instead, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B, H, N_TOK, D = 4, 32, 32768, 128
+SEED = 2024
+# Algorithmic work per (token, head) at d = e = 128, bf16, forward + backward: bytes that must cross HBM
+# (read q,k,v / write o; read q,k,v,do / write dq,dk,dv) and flops with the reference's 64-token blocks.
+ALG_BYTES_PER_UNIT = 2816
+ALG_FLOP_PER_UNIT = 344064
+LA_LAUNCHES_PER_STEP = 4  # forward, dq, dk, dv: four launches of the same block kernel
+# DRAM bytes (read + write) per launch of la_chunk_kernel measured with ncu; see profiles/. None = not captured yet.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_sample(pairs):
+    """fwd+bwd of `pairs` (batch, head) units at full sequence length with the numpy oracle (fp32), one unit per
+    host thread (BLAS pinned to one thread per worker); returns (seconds, tokens/s scaled to the full b*h workload)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    import numpy as np
+    from oracle import lightning_oracle as O
+
+    rng = np.random.default_rng(SEED)
+    q, k, v, do = (rng.standard_normal((pairs, 1, N_TOK, D)).astype(np.float32) for _ in range(4))
+    slopes = O.build_slopes(H)
+
+    def one(i):
+        s = slopes[i % H:i % H + 1]
+        O.la2_fwd_blockwise(q[i:i + 1], k[i:i + 1], v[i:i + 1], s, dtype=np.float32)
+        O.la2_bwd_blockwise(q[i:i + 1], k[i:i + 1], v[i:i + 1], s, do[i:i + 1], dtype=np.float32)
+
+    try:
+        from threadpoolctl import threadpool_limits
+        limiter = threadpool_limits(limits=1)
+    except Exception:
+        limiter = None
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=min(pairs, host_threads())) as pool:
+        list(pool.map(one, range(pairs)))
+    dt = time.perf_counter() - t0
+    if limiter is not None:
+        limiter.restore_original_limits()
+    tokens = B * N_TOK * (pairs / float(B * H))  # share of the step's tokens this sample stands for
+    return dt, tokens / dt
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    pairs = host_threads()
+    for _ in range(args.warmup):
+        cpu_sample(pairs)
+    times = [cpu_sample(pairs)[0] for _ in range(args.steps)]
+    dt = sum(times) / len(times)
+    value = B * N_TOK * (pairs / float(B * H)) / dt
+    sample = (f"{pairs} of {B * H} (batch, head) pairs at n={N_TOK}, d=e={D}, fp32 numpy block recurrences, fwd+bwd, "
+              "one pair per host thread, scaled to the full step")
+    print(json.dumps({
+        "impl": "reference", "metric": "lightning2_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"lightning2 fwd+bwd b{B} h{H} n{N_TOK} d{D} e{D} per GPU, decay slopes", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": host_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--n", type=int, default=N_TOK, help="sequence length (default: the benchmark's largest point)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    global N_TOK
+    N_TOK = args.n
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import lightning_attention_b200 as la
+    from lightning_attention_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU (the product has no CPU path); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- synthetic inputs, resident in HBM (4 x 1.07 GB, far larger than the 126 MB L2) ----------------
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED + rank)
+    mk = lambda: torch.randn((B, H, N_TOK, D), device=dev, dtype=torch.float32, generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(), mk(), mk(), mk()
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    s = la._build_slope_tensor(H).to(dev)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        o = la.lightning_attn2(q, k, v, s)
+        o.backward(do)
+        return o
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches0 = L.lab200_launch_count()
+    barrier()
+    for i in range(args.steps):
+        q.grad = k.grad = v.grad = None
+        ev[i][0].record()
+        o = la.lightning_attn2(q, k, v, s)
+        ev[i][1].record()
+        o.backward(do)
+        ev[i][2].record()
+    end = torch.cuda.Event(enable_timing=True)
+    end.record()
+    barrier()
+    launches = L.lab200_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = ev[0][0].elapsed_time(end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, bwd_ms = (float(x) for x in t)
+    ms_per_step = total_ms / args.steps
+    tokens_per_step = B * N_TOK * world
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- SRMSNorm fwd+bwd GB/s on (32768, 4096) bf16 (rank 0) -------------------------------------------
+    srms = None
+    if rank == 0:
+        M, Nf = 4 * 8192, 4096
+        x = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g).requires_grad_()
+        dy = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g)
+        norm = la.SimpleRMSNorm(Nf)
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        tf, tb = [], []
+        for i in range(8):
+            x.grad = None
+            flush.zero_()
+            a, b_, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            a.record(); y = norm(x); b_.record(); y.backward(dy); c.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                tf.append(a.elapsed_time(b_)); tb.append(b_.elapsed_time(c))
+        fms, bms = statistics.median(tf), statistics.median(tb)
+        srms = {"shape": [M, Nf], "fwd_ms": fms, "bwd_ms": bms, "fwd_gbs": 4.0 * M * Nf / fms / 1e6,
+                "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API incl. autograd overhead; L2 flushed between reps"}
+        del x, dy, flush
+
+    # ---- end to end through the public API with pinned host buffers ---------------------------------------
+    e2e = None
+    nbytes = q.numel() * 2
+    try:
+        if args.no_e2e:
+            raise RuntimeError("skipped by --no-e2e")
+        hq, hk, hv, hdo = (torch.empty((B, H, N_TOK, D), dtype=torch.bfloat16, pin_memory=True) for _ in range(4))
+        ho, hdq, hdk, hdv = (torch.empty((B, H, N_TOK, D), dtype=torch.bfloat16, pin_memory=True) for _ in range(4))
+        for hsrc, dsrc in ((hq, q), (hk, k), (hv, v), (hdo, do)):
+            hsrc.copy_(dsrc.detach())
+        dq_, dk_, dv_, ddo_ = (torch.empty_like(do) for _ in range(4))
+
+        def e2e_step():
+            dq_.copy_(hq, non_blocking=True); dk_.copy_(hk, non_blocking=True)
+            dv_.copy_(hv, non_blocking=True); ddo_.copy_(hdo, non_blocking=True)
+            qq, kk, vv = dq_.requires_grad_(), dk_.requires_grad_(), dv_.requires_grad_()
+            qq.grad = kk.grad = vv.grad = None
+            oo = la.lightning_attn2(qq, kk, vv, s)
+            oo.backward(ddo_)
+            ho.copy_(oo.detach(), non_blocking=True); hdq.copy_(qq.grad, non_blocking=True)
+            hdk.copy_(kk.grad, non_blocking=True); hdv.copy_(vv.grad, non_blocking=True)
+            dq_.requires_grad_(False); dk_.requires_grad_(False); dv_.requires_grad_(False)
+
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0]) / args.e2e_steps
+        e2e = {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes,
+               "note": "q,k,v,do copied from pinned host memory and o,dq,dk,dv copied back every step, per rank"}
+    except Exception as ex:  # pinned allocation can fail on a small host
+        e2e = {"value": None, "unit": "tokens/s", "error": repr(ex)[:200]}
+
+    if rank == 0:
+        hbm_peak, tf_peak, peak_kind = load_peaks()
+        units = B * H * N_TOK
+        launch_ms = (fwd_ms + bwd_ms) / LA_LAUNCHES_PER_STEP
+        achieved = ALG_BYTES_PER_UNIT * units / LA_LAUNCHES_PER_STEP / (launch_ms * 1e-3) / 1e9
+        roofline = {
+            "bound": "hbm", "kernel": "la_chunk_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+            "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+            "launch_ms": launch_ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "alg_tflops": ALG_FLOP_PER_UNIT * units / ((fwd_ms + bwd_ms) * 1e-3) / 1e12,
+            "frac_tensor": ALG_FLOP_PER_UNIT * units / ((fwd_ms + bwd_ms) * 1e-3) / 1e12 / tf_peak,
+        }
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            pairs = 2 * host_threads()
+            dt, tps = cpu_sample(pairs)
+            cpu = {"value": tps, "unit": "tokens/s", "cores": host_threads(), "kind": "port", "seconds": dt,
+                   "sample": f"{pairs} of {B * H} (batch, head) pairs at n={N_TOK}, fp32 numpy block recurrences, fwd+bwd, one pair per host thread, scaled to the full step"}
+        out = {
+            "metric": "lightning2_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"lightning2 fwd+bwd b{B} h{H} n{N_TOK} d{D} e{D} per GPU, decay slopes",
+                       "l2": "inputs (4 x 1.07 GB) exceed L2; no flush needed", "parallelism": f"bh-shard x{world}, no collective"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "srmsnorm": srms,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

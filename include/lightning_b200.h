@@ -45,6 +45,10 @@ extern "C" {
 /* Library version, major * 10000 + minor * 100 + patch. */
 int lab200_version(void);
 
+/* Number of CUDA kernels this library has launched in this process so far (all entry points,
+ * all streams). Bookkeeping for benchmarks; no counterpart in the reference. */
+long long lab200_launch_count(void);
+
 /* Static, human-readable text for an error code. */
 const char* lab200_error_string(int code);
 

@@ -5,6 +5,7 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/lightning_b200.h"
@@ -18,6 +19,8 @@ namespace {
 constexpr size_t WS_HEADER = 256;            // status block in front of the workspace
 constexpr int SMEM_LIMIT = 232448;           // 227 KB opt-in dynamic shared memory per CTA
 constexpr long long WAIT_BUDGET = 2000000000LL;  // ~1 s of SM clocks per barrier wait
+
+std::atomic<long long> g_launches{0};  // kernels launched by this library since load
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -102,6 +105,7 @@ int launch_one(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& 
     return LAB200_ERR_CUDA;
   }
   kern<<<grid, LA_THREADS, smem, st>>>(tA, tB, tC, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
 }
 
@@ -206,6 +210,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
   la_scan_kernel<<<blocks, threads, 0, st>>>(states, state_in, state_out, slopes, h, nchunks, elems, nblocks, bpc,
                                              p.reverse, skip_last, total);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
   if (state_only) return LAB200_OK;
 
@@ -243,6 +248,7 @@ void srms_launch(bool fwd, const void* x, const void* dy, void* out, float* rstd
   constexpr int CTA = (G > 256 ? G : 256);
   constexpr int RPC = CTA / G;
   const unsigned grid = static_cast<unsigned>((M + RPC - 1) / RPC);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   if (fwd) {
     srmsnorm_fwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, out, rstd, static_cast<int>(M), N, eps);
   } else {
@@ -257,6 +263,7 @@ int srms_dispatch(bool fwd, const void* x, const void* dy, void* out, float* rst
   const bool vec_ok = (N % EPV == 0) && aligned16(x) && aligned16(out) && (fwd || aligned16(dy));
   if (!vec_ok) {
     const unsigned grid = static_cast<unsigned>(M);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     if (fwd) {
       srmsnorm_fwd_generic_kernel<DT><<<grid, 256, 0, st>>>(x, out, rstd, static_cast<int>(M), N, eps);
     } else {
@@ -299,6 +306,8 @@ int srms_entry(bool fwd, const void* x, const void* dy, void* out, float* rstd, 
 extern "C" {
 
 int lab200_version(void) { return 100; }
+
+long long lab200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* lab200_error_string(int code) {
   switch (code) {

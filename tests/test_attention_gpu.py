@@ -1,0 +1,246 @@
+"""GPU parity tests of the attention path. Everything goes through the C ABI (ctypes), either directly or
+via the autograd Functions. References: the numpy oracle (small sizes), the golden fixtures generated
+from the reference, and an fp32 torch restatement of the block recurrence (large sizes)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import lightning_attention_b200 as la
+from lightning_attention_b200 import _lib
+from lightning_attention_b200.ops.cuda.lightning_attn2 import la_generic
+from oracle import lightning_oracle as O
+
+from _refs import assert_parity, errs, geometric_slopes, torch_la_reference
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+# the reference's own shape list, tests/ops/test_lightning2.py:9-28
+REF_SHAPES = [
+    (6, 8, 256, 128, 64), (6, 8, 512, 128, 64), (6, 8, 1024, 128, 64), (6, 8, 2048, 128, 64),
+    (6, 8, 4096, 128, 64), (6, 8, 8192, 128, 64), (6, 8, 2048, 32, 64), (6, 8, 2048, 64, 64),
+    (6, 12, 2048, 128, 64), (6, 16, 2048, 128, 64), (6, 20, 2048, 128, 64), (1, 8, 2048, 128, 64),
+    (2, 8, 2048, 128, 64), (3, 8, 2048, 128, 64), (6, 8, 913, 128, 64), (6, 8, 513, 128, 64),
+    (6, 8, 1213, 128, 64), (6, 8, 2048, 16, 64),
+]
+
+
+def make_inputs(b, h, n, d, e, dtype, scale, seed=2024):
+    torch.manual_seed(seed)
+    q = (torch.randn((b, h, n, d), device=DEV) * scale).to(dtype).requires_grad_()
+    k = (torch.randn((b, h, n, d), device=DEV) * scale).to(dtype).requires_grad_()
+    v = (torch.randn((b, h, n, e), device=DEV) * scale).to(dtype).requires_grad_()
+    do = (torch.randn((b, h, n, e), device=DEV) * scale).to(dtype)
+    return q, k, v, do
+
+
+def run_fwd_bwd(fn, q, k, v, do):
+    o = fn(q, k, v)
+    o.backward(do)
+    grads = (q.grad, k.grad, v.grad)
+    q.grad = k.grad = v.grad = None
+    return (o.detach(),) + tuple(g.detach() for g in grads)
+
+
+def compare_with_torch_reference(q, k, v, do, s, got, scaled, tag):
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = run_fwd_bwd(lambda a, b_, c: torch_la_reference(a, b_, c, s), qr, kr, vr, do.float())
+    for x, r, name in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert_parity(x, r, f"{tag}:{name}", scaled)
+
+
+@pytest.mark.parametrize("b,h,n,d,e", REF_SHAPES)
+def test_reference_shape_list_bf16(cuda_lib, b, h, n, d, e):
+    """Same shapes, seed, randn/10 inputs and slopes as tests/ops/test_lightning2.py:33-58, with real assertions."""
+    q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 0.1)
+    s = la._build_slope_tensor(h).to(DEV)
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2(a, b_, c, s), q, k, v, do)
+    compare_with_torch_reference(q, k, v, do, s, got, True, f"decay{(b, h, n, d, e)}")
+
+
+@pytest.mark.parametrize("b,h,n,d,e", [REF_SHAPES[i] for i in (0, 3, 6, 14, 15, 17)])
+def test_reference_shape_list_no_decay_bf16(cuda_lib, b, h, n, d, e):
+    """tests/ops/test_lightning2_no_decay.py:31-56 (s=None), subset of its shape list."""
+    q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 0.1)
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2_no_decay(a, b_, c), q, k, v, do)
+    compare_with_torch_reference(q, k, v, do, None, got, True, f"nodecay{(b, h, n, d, e)}")
+
+
+@pytest.mark.parametrize("slopes", ["formula", "build"])
+def test_readme_example_config(cuda_lib, slopes):
+    """b2 h12 n2048 d=e=192 bf16, N(0,1) inputs, loss = o.sum(), through lightning_attn_func
+    (examples/ops/example_lightning_attn.py)."""
+    b, h, n, d, e = 2, 12, 2048, 192, 192
+    q, k, v, _ = make_inputs(b, h, n, d, e, torch.bfloat16, 1.0)
+    s = (geometric_slopes(h, DEV) if slopes == "formula" else la._build_slope_tensor(h).to(DEV))
+    do = torch.ones((b, h, n, e), device=DEV, dtype=torch.bfloat16)
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn_func(a, b_, c, s), q, k, v, do)
+    compare_with_torch_reference(q, k, v, do, s, got, False, f"readme-{slopes}")
+
+
+@pytest.mark.parametrize("n", [512, 2048, 8192])
+@pytest.mark.parametrize("decay", [True, False])
+def test_benchmark_config_small_n(cuda_lib, n, decay):
+    """b4 h32 d=e=128 bf16 N(0,1) (benchmarks/benchmark_lightning2.py:99-102), with and without decay."""
+    b, h, d = 4, 32, 128
+    q, k, v, do = make_inputs(b, h, n, d, d, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(h).to(DEV) if decay else None
+    fn = (lambda a, b_, c: la.lightning_attn_func(a, b_, c, s))
+    got = run_fwd_bwd(fn, q, k, v, do)
+    compare_with_torch_reference(q, k, v, do, s, got, False, f"bench-n{n}-decay{decay}")
+
+
+def test_benchmark_config_full_size_sampled(cuda_lib):
+    """b4 h32 n32768 d=e=128: the whole tensor is computed; three (batch, head) pairs are checked against the
+    fp32 recurrence, and the result must be linear in v (a size-independent property)."""
+    b, h, n, d = 4, 32, 32768, 128
+    q, k, v, do = make_inputs(b, h, n, d, d, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(h).to(DEV)
+    o, dq, dk, dv = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2(a, b_, c, s), q, k, v, do)
+    for (ib, ih) in ((0, 0), (1, 17), (3, 31)):
+        sl = (slice(ib, ib + 1), slice(ih, ih + 1))
+        qs, ks, vs, dos = (t[sl].detach() for t in (q, k, v, do))
+        qr, kr, vr = (t.float().requires_grad_() for t in (qs, ks, vs))
+        ref = run_fwd_bwd(lambda a, b_, c: torch_la_reference(a, b_, c, s[ih:ih + 1]), qr, kr, vr, dos.float())
+        for x, r, name in zip((o, dq, dk, dv), ref, ("o", "dq", "dk", "dv")):
+            assert_parity(x[sl], r, f"full-size({ib},{ih}):{name}", False)
+    with torch.no_grad():
+        o2 = la.lightning_attn2(q, k, (2 * v.detach()).to(torch.bfloat16), s)  # exact doubling in bf16
+    assert torch.equal(o2.float(), 2 * o.float())
+
+
+def c_generic(cuda_lib, a, bm, c, s, reverse, state_in, want_state, chunks, state_only=False):
+    """Direct ctypes call of lab200_la_generic with raw pointers (no Python op layer in between)."""
+    b, h, n, dk = bm.shape
+    dv = c.shape[-1]
+    out = None if state_only else torch.empty((b, h, n, dv), dtype=bm.dtype, device=DEV)
+    st = torch.empty((b, h, dv, dk), dtype=torch.float32, device=DEV) if (want_state or state_only) else None
+    nbytes = cuda_lib.lab200_la_workspace_bytes(b * h, n, dk, dv, chunks)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    rc = cuda_lib.lab200_la_generic(
+        _lib.ptr(a), bm.data_ptr(), c.data_ptr(), _lib.ptr(s), _lib.ptr(out), _lib.ptr(state_in), _lib.ptr(st),
+        ws.data_ptr(), nbytes, b * h, h, n, dk, dv, int(reverse), int(state_only), chunks, _lib.dtype_code(bm.dtype),
+        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, cuda_lib.lab200_error_string(rc)
+    assert cuda_lib.lab200_read_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    return out, st
+
+
+ORACLE_CASES = [
+    # b, h, n, dk, dv, reverse, chunks, with_state
+    (1, 2, 128, 64, 64, False, 1, False),
+    (1, 2, 256, 128, 128, False, 1, True),
+    (2, 3, 384, 128, 64, True, 1, True),
+    (1, 2, 512, 64, 128, False, 2, True),
+    (1, 2, 512, 128, 128, True, 4, True),
+    (1, 3, 300, 16, 48, False, 1, False),
+    (1, 3, 77, 48, 16, True, 1, False),
+    (1, 2, 384, 192, 192, False, 3, True),
+    (1, 2, 256, 256, 256, True, 2, True),
+    (1, 1, 1, 16, 16, False, 1, False),
+    (1, 1, 129, 32, 32, True, 2, False),
+]
+
+
+@pytest.mark.parametrize("b,h,n,dk,dv,reverse,chunks,with_state", ORACLE_CASES)
+@pytest.mark.parametrize("slope_scale", [1.0, 0.0])
+def test_c_abi_generic_against_numpy_oracle(cuda_lib, b, h, n, dk, dv, reverse, chunks, with_state, slope_scale):
+    torch.manual_seed(7)
+    a, bm = (torch.randn((b, h, n, dk), device=DEV).bfloat16() for _ in range(2))
+    c = torch.randn((b, h, n, dv), device=DEV).bfloat16()
+    s = (la._build_slope_tensor(h).reshape(-1) * slope_scale).to(DEV) if slope_scale > 0 else None
+    aligned = (n % 128 == 0)
+    st_in = torch.randn((b, h, dv, dk), device=DEV) if (with_state and aligned) else None
+    out, st = c_generic(cuda_lib, a, bm, c, s, reverse, st_in, aligned, chunks)
+    f = lambda t: None if t is None else t.float().cpu().numpy()
+    ro, rs = O.la_generic(f(a), f(bm), f(c), f(s), reverse=reverse, state_in=f(st_in))
+    assert O.rel_l2_err(f(out), ro) <= 1e-2
+    assert O.max_abs_err(f(out), ro) <= 2e-2 * max(1.0, float(np.abs(ro).max()))
+    if aligned:
+        assert O.rel_l2_err(f(st), rs) <= 1e-2
+        # state-only mode returns the same state
+        _, st2 = c_generic(cuda_lib, None, bm, c, s, reverse, st_in, True, chunks, state_only=True)
+        assert O.rel_l2_err(f(st2), rs) <= 1e-2
+
+
+@pytest.mark.parametrize("name", ["attn_c1_fp32_sum", "attn_ragged_fp32", "attn_nodecay_fp32", "attn_bf16_div10"])
+def test_against_golden_fixtures(cuda_lib, golden_dir, name):
+    """Outputs of the reference's torch path (stored fixtures) vs the CUDA path on the same inputs rounded to bf16."""
+    g = dict(np.load(os.path.join(golden_dir, name + ".npz")))
+    q, k, v = (torch.from_numpy(g[x]).to(DEV).bfloat16().requires_grad_() for x in ("q", "k", "v"))
+    do = torch.from_numpy(g["do"]).to(DEV).bfloat16()
+    s = torch.from_numpy(g["s"]).to(DEV).reshape(-1, 1, 1) if "s" in g else None
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn_func(a, b_, c, s), q, k, v, do)
+    scaled = name.endswith("div10")
+    for x, key in zip(got, ("o", "dq", "dk", "dv")):
+        assert_parity(x, torch.from_numpy(g[key]).to(DEV), f"{name}:{key}", scaled)
+
+
+def test_chunked_and_serial_sweeps_agree(cuda_lib):
+    b, h, n, d = 1, 4, 4096, 128
+    q, k, v, _ = make_inputs(b, h, n, d, d, torch.bfloat16, 1.0)
+    s = (la._build_slope_tensor(h).reshape(-1) * 0.01).to(DEV)  # slow decay: the carried state matters everywhere
+    ref = torch_la_reference(q.detach(), k.detach(), v.detach(), s)
+    for chunks in (1, 2, 5, 16):
+        out, _ = la_generic(q.detach(), k.detach(), v.detach(), s, chunks=chunks)
+        assert_parity(out, ref, f"chunks={chunks}", False)
+
+
+def test_known_answers_on_gpu(cuda_lib):
+    n, d, e = 1000, 16, 16
+    q = torch.full((1, 1, n, d), 0.25, device=DEV, dtype=torch.bfloat16)  # 1/sqrt(16)
+    v = torch.ones((1, 1, n, e), device=DEV, dtype=torch.bfloat16)
+    o = la.lightning_attn_func(q, q, v, None).float()
+    # o_t = t + 1 exactly representable in fp32; bf16 output rounding allows 2^-8 relative
+    t = torch.arange(1, n + 1, device=DEV, dtype=torch.float32)
+    assert float(((o[0, 0, :, 0] - t).abs() / t).max()) <= 2 ** -8
+    q1 = torch.zeros((1, 1, n, d), device=DEV, dtype=torch.bfloat16)
+    q1[..., 0] = 1
+    s = torch.tensor([0.25], device=DEV).reshape(1, 1, 1)
+    o = la.lightning_attn_func(q1, q1, q1, s).float()[0, 0, :, 0]
+    lam = float(np.exp(-0.25))
+    expect = (1 - lam ** t) / (1 - lam)
+    assert float(((o - expect).abs() / expect).max()) <= 1e-2
+
+
+def test_bitwise_determinism(cuda_lib):
+    q, k, v, do = make_inputs(2, 4, 1500, 64, 128, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(4).to(DEV)
+    r1 = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2(a, b_, c, s), q, k, v, do)
+    r2 = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2(a, b_, c, s), q, k, v, do)
+    for x, y in zip(r1, r2):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("n", [1, 2, 127, 128, 129, 255, 257])
+def test_ragged_lengths(cuda_lib, n):
+    q, k, v, do = make_inputs(2, 2, n, 32, 64, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(2).to(DEV)
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2(a, b_, c, s), q, k, v, do)
+    compare_with_torch_reference(q, k, v, do, s, got, False, f"n={n}")
+
+
+@pytest.mark.parametrize("d,e", [(24, 40), (16, 16), (96, 80), (160, 208), (256, 256), (320, 64)])
+def test_interface_pads_and_splits_feature_dims(cuda_lib, d, e):
+    """lightning_attn_func accepts sizes that are not multiples of 16 (zero padding) and d > 256 (feature split),
+    the counterpart of the reference's pad/split wrapper (lightning_attn_interface.py:28-63)."""
+    q, k, v, do = make_inputs(1, 2, 300, d, e, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(2).to(DEV)
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn_func(a, b_, c, s), q, k, v, do)
+    assert got[0].shape == (1, 2, 300, e)
+    compare_with_torch_reference(q, k, v, do, s, got, False, f"d{d}e{e}")
+
+
+def test_non_contiguous_inputs_and_no_grad_for_slopes(cuda_lib):
+    b, h, n, d = 2, 3, 200, 64
+    torch.manual_seed(3)
+    qkv = torch.randn((b, n, 3, h, d), device=DEV).bfloat16()
+    q, k, v = (qkv[:, :, i].transpose(1, 2).requires_grad_() for i in range(3))  # (b, h, n, d) views
+    s = la._build_slope_tensor(h).to(DEV).requires_grad_()
+    o = la.lightning_attn_func(q, k, v, s)
+    o.sum().backward()
+    assert s.grad is None and q.grad is not None
+    ref = torch_la_reference(q.detach(), k.detach(), v.detach(), s.detach())
+    assert_parity(o, ref, "non-contiguous", False)
