@@ -163,6 +163,7 @@ def run_reference(args, rank):
 
 
 def main():
+    global N_TOK
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -174,7 +175,6 @@ def main():
     ap.add_argument("--n", type=int, default=N_TOK, help="sequence length (default: the benchmark's largest point)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    global N_TOK
     N_TOK = args.n
 
     rank = int(os.environ.get("RANK", "0"))
