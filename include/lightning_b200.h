@@ -49,6 +49,13 @@ int lab200_version(void);
  * all streams). Bookkeeping for benchmarks; no counterpart in the reference. */
 long long lab200_launch_count(void);
 
+/* Profiling aid, off by default: while `device_buffer` is non-NULL, CTA (0,0,0) of every attention
+ * block kernel writes clock64() at six points of each of its first `blocks` 128-token blocks into
+ * device_buffer[block * 6 + point] (points: block start, inputs landed, first MMA group done, masked
+ * tile stored, second MMA group done, epilogue done). Pass NULL to switch it off. No counterpart
+ * in the reference. */
+void lab200_la_debug_trace(long long* device_buffer, int blocks);
+
 /* Static, human-readable text for an error code. */
 const char* lab200_error_string(int code);
 

@@ -28,6 +28,8 @@ def lib():
         L.lab200_version.argtypes = []
         L.lab200_launch_count.restype = ll
         L.lab200_launch_count.argtypes = []
+        L.lab200_la_debug_trace.restype = None
+        L.lab200_la_debug_trace.argtypes = [vp, i]
         L.lab200_error_string.restype = ctypes.c_char_p
         L.lab200_error_string.argtypes = [i]
         L.lab200_la_plan_chunks.restype = i
@@ -51,7 +53,7 @@ def lib():
 
 
 EXPORTS = [
-    "lab200_version", "lab200_launch_count", "lab200_error_string", "lab200_la_plan_chunks", "lab200_la_workspace_bytes",
+    "lab200_version", "lab200_launch_count", "lab200_la_debug_trace", "lab200_error_string", "lab200_la_plan_chunks", "lab200_la_workspace_bytes",
     "lab200_la_generic", "lab200_la2_fwd", "lab200_la2_bwd", "lab200_read_status",
     "lab200_srmsnorm_fwd", "lab200_srmsnorm_bwd",
 ]

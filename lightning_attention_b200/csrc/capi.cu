@@ -21,6 +21,8 @@ constexpr int SMEM_LIMIT = 232448;           // 227 KB opt-in dynamic shared mem
 constexpr long long WAIT_BUDGET = 2000000000LL;  // ~1 s of SM clocks per barrier wait
 
 std::atomic<long long> g_launches{0};  // kernels launched by this library since load
+std::atomic<long long*> g_trace{nullptr};  // optional device buffer for per-block clock stamps
+std::atomic<int> g_trace_blocks{0};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -79,7 +81,7 @@ int smem_bytes(int nks, int nvs, int mode, int nstage) {
   const int slab = LA_SLAB_BYTES;
   int b = nstage * (nks + 2) * slab;
   if (mode == 0) b += nks * slab + 2 * slab + nks * nvs * 64 * 128;
-  return b + 64 + 1024;  // barriers + alignment slack
+  return b + 64 + 512 + 1024;  // barriers + decay table + alignment slack
 }
 
 int plan_chunks(int bh, int n, int dk, int dv) {
@@ -185,6 +187,8 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   p.reverse = reverse ? 1 : 0;
   p.nstage = 2;
   p.wait_budget = WAIT_BUDGET;
+  p.trace = g_trace.load(std::memory_order_relaxed);
+  p.trace_blocks = g_trace_blocks.load(std::memory_order_relaxed);
 
   if (nchunks == 1) {
     p.chunk0 = 0;
@@ -306,6 +310,11 @@ int srms_entry(bool fwd, const void* x, const void* dy, void* out, float* rstd, 
 extern "C" {
 
 int lab200_version(void) { return 100; }
+
+void lab200_la_debug_trace(long long* device_buffer, int blocks) {
+  g_trace_blocks.store(device_buffer ? blocks : 0, std::memory_order_relaxed);
+  g_trace.store(device_buffer, std::memory_order_relaxed);
+}
 
 long long lab200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -61,6 +61,8 @@ struct LaParams {
   int reverse;
   int nstage;              // 1 or 2 shared-memory stages for the Bm and C tiles
   long long wait_budget;   // clock cycles after which a barrier wait gives up
+  long long* trace;        // optional: CTA (0,0,0) records clock64() at 6 points per block here
+  int trace_blocks;        // capacity of `trace` in blocks
 };
 
 template <int FMT>
@@ -113,6 +115,9 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const uint32_t sBar = sS + (MODE == 0 ? NKS * DV * 128 : 0);
   const uint32_t barA = sBar, barBC0 = sBar + 8, barM1 = sBar + 24, barM2 = sBar + 32;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sBar + 40 - raw));
+  // decay table lambda^k, k = 0..127, for the in-block mask (a table look-up per element instead of an
+  // exponential; also keeps the compiler from hoisting 64 exponentials per thread into registers)
+  volatile float* decay_tab = reinterpret_cast<volatile float*>(smem_raw + (sBar + 64 - raw));
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -158,6 +163,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const float w_out = reverse ? w_bwd : w_fwd;
   const float w_state = reverse ? w_fwd : w_bwd;
   const float decay_blk = ex2f(s2 * static_cast<float>(LA_BLOCK));
+  if (MODE == 0 && tid < LA_BLOCK) decay_tab[tid] = ex2f(s2 * static_cast<float>(tid));
 
   auto issue_A = [&](int blk) {
     mbar_arrive_expect_tx(barA, NKS * SLAB);
@@ -218,8 +224,11 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   __syncthreads();
 
   int failed = 0;
+  const bool tracing = (p.trace != nullptr) && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#define LA_TRACE(slot) if (tracing && it < p.trace_blocks) p.trace[it * 6 + (slot)] = clock64();
 
   for (int it = 0; it < nb; ++it) {
+    LA_TRACE(0)
     const int blk = reverse ? (blk_end - 1 - it) : (blk_begin + it);
     const int nxt = reverse ? (blk - 1) : (blk + 1);
     const bool has_next = (it + 1 < nb);
@@ -236,6 +245,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (MODE == 0) ok = ok && mbar_wait(barA, par, p.wait_budget);
       if (__syncthreads_or(!ok)) { failed = LA_ERR_WAIT_INPUT; break; }
     }
+    LA_TRACE(1)
 
     if (MODE == 0) {
       if (tid == 0) {
@@ -258,6 +268,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const bool ok = mbar_wait(barM1, par, p.wait_budget);
         if (__syncthreads_or(!ok)) { failed = LA_ERR_WAIT_MMA1; break; }
       }
+      LA_TRACE(2)
       tc_fence_after_sync();
       if (tid == 0 && has_next) {
         issue_A(nxt);
@@ -280,8 +291,8 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (!dead) {
             const int d0 = reverse ? (c0 + i - r) : (r - c0 - i);  // distance on the causal side when >= 0
             const int d1 = reverse ? (d0 + 1) : (d0 - 1);
-            f0 = (d0 >= 0) ? __uint_as_float(v[i]) * ex2f(s2 * static_cast<float>(d0)) : 0.f;
-            f1 = (d1 >= 0) ? __uint_as_float(v[i + 1]) * ex2f(s2 * static_cast<float>(d1)) : 0.f;
+            if (d0 >= 0) f0 = __uint_as_float(v[i]) * decay_tab[d0];
+            if (d1 >= 0) f1 = __uint_as_float(v[i + 1]) * decay_tab[d1];
           }
           pk[i >> 1] = pack2<FMT>(f0, f1);
         }
@@ -314,6 +325,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
+    LA_TRACE(3)
 
     // ---- 3. O_intra = P C ; StateT_local = C^T (w_state Bm) ------------------------------------
     if (tid == 0) {
@@ -336,6 +348,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const bool ok = mbar_wait(barM2, par, p.wait_budget);
       if (__syncthreads_or(!ok)) { failed = LA_ERR_WAIT_MMA2; break; }
     }
+    LA_TRACE(4)
     tc_fence_after_sync();
     if (tid == 0 && has_next && nstage == 1) issue_BC(nxt, 0);
 
@@ -384,7 +397,9 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
+    LA_TRACE(5)
   }
+#undef LA_TRACE
 
   if (!failed && p.state_out != nullptr && st_row_valid) {
     float* dst = p.state_out +
