@@ -273,6 +273,44 @@ def main():
                 "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API incl. autograd overhead; L2 flushed between reps"}
         del x, dy, flush
 
+    # ---- long-context leg: b=1, h=32, d=e=128, 131072 tokens per GPU (the sequence-parallel shard size) ----
+    # N = 1: plain single-GPU op at n = 131072. N > 1: sequence-parallel over N*131072 tokens (two NCCL
+    # all-gathers of 2 MiB states per step). Same per-GPU work in both, so the ratio of the two times is the
+    # sequence-parallel overhead.
+    sp = None
+    if args.n == 32768:
+        try:
+            from lightning_attention_b200 import distributed as D
+
+            Ls = 131072
+            mk2 = lambda: (0.5 * torch.randn((1, H, Ls, D), device=dev, dtype=torch.float32, generator=g)).to(torch.bfloat16)
+            q2, k2, v2, do2 = mk2(), mk2(), mk2(), mk2()
+            q2.requires_grad_(); k2.requires_grad_(); v2.requires_grad_()
+
+            def sp_step():
+                q2.grad = k2.grad = v2.grad = None
+                o2 = D.lightning_attn_sp(q2, k2, v2, s) if world > 1 else la.lightning_attn2(q2, k2, v2, s)
+                o2.backward(do2)
+
+            for _ in range(3):
+                sp_step()
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(5):
+                sp_step()
+            a1.record()
+            barrier()
+            tt = torch.tensor([a0.elapsed_time(a1) / 5], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            sp = {"mode": "sequence-parallel" if world > 1 else "single-gpu", "tokens_total": Ls * world,
+                  "ms_per_step": float(tt[0]), "tokens_per_s": Ls * world / (float(tt[0]) * 1e-3),
+                  "shape_per_gpu": [1, H, Ls, D]}
+            del q2, k2, v2, do2
+        except Exception as ex:
+            sp = {"error": repr(ex)[:200]}
+
     # ---- end to end through the public API with pinned host buffers ---------------------------------------
     e2e = None
     nbytes = q.numel() * 2
@@ -339,7 +377,7 @@ def main():
             "config": {"workload": f"lightning2 fwd+bwd b{B} h{H} n{N_TOK} d{D} e{D} per GPU, decay slopes",
                        "l2": "inputs (4 x 1.07 GB) exceed L2; no flush needed", "parallelism": f"bh-shard x{world}, no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "srmsnorm": srms,
+            "srmsnorm": srms, "long_context": sp,
         }
         print(json.dumps(out), flush=True)
     if world > 1:

@@ -244,3 +244,36 @@ def test_non_contiguous_inputs_and_no_grad_for_slopes(cuda_lib):
     assert s.grad is None and q.grad is not None
     ref = torch_la_reference(q.detach(), k.detach(), v.detach(), s.detach())
     assert_parity(o, ref, "non-contiguous", False)
+
+
+@pytest.mark.parametrize("scale", [1.0, 1e-3, 0.0])
+def test_sequence_parallel_math_on_one_gpu(cuda_lib, scale):
+    """The sequence-parallel scheme run rank by rank on one GPU (no process group): local states from the CUDA
+    state-only pass, combined with the package's own `combine_states`, fed back as incoming states, must
+    reproduce the unsharded CUDA result and the fp32 reference, forward and backward."""
+    from lightning_attention_b200 import distributed as D
+
+    b, h, R, L, d, e = 1, 4, 4, 256, 128, 64
+    n = R * L
+    q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 0.5)
+    q, k, v = (t.detach() for t in (q, k, v))
+    s = (la._build_slope_tensor(h) * scale).to(DEV) if scale > 0 else None
+    decay = D._shard_decay(s, h, L, q.device)
+    sl = [slice(r * L, (r + 1) * L) for r in range(R)]
+    cut = lambda t, r: t[:, :, sl[r]].contiguous()
+    fwd_states = [la_generic(None, cut(k, r), cut(v, r), s, state_only=True)[1] for r in range(R)]
+    rev_states = [la_generic(None, cut(do, r), cut(q, r), s, reverse=True, state_only=True)[1] for r in range(R)]
+    o, dq, dk, dv = [], [], [], []
+    for r in range(R):
+        kv_in = D.combine_states(fwd_states, decay, r)
+        dkv_in = D.combine_states(rev_states, decay, r, reverse=True)
+        o.append(la_generic(cut(q, r), cut(k, r), cut(v, r), s, state_in=kv_in)[0])
+        dq.append(la_generic(cut(do, r), cut(v, r), cut(k, r), s, state_in=kv_in.transpose(2, 3).contiguous())[0])
+        dk.append(la_generic(cut(v, r), cut(do, r), cut(q, r), s, reverse=True, state_in=dkv_in)[0])
+        dv.append(la_generic(cut(k, r), cut(q, r), cut(do, r), s, reverse=True,
+                             state_in=dkv_in.transpose(2, 3).contiguous())[0])
+    got = tuple(torch.cat(x, dim=2) for x in (o, dq, dk, dv))
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref = run_fwd_bwd(lambda a, b_, c: torch_la_reference(a, b_, c, s), qr, kr, vr, do.float())
+    for x, r_, name in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert_parity(x, r_, f"sp-emulated:{name}", False)
