@@ -38,6 +38,10 @@ extern "C" {
 #define LAB200_ERR_CUDA 4        /* a CUDA runtime call or launch failed */
 #define LAB200_ERR_DRIVER 5      /* the driver lacks cuTensorMapEncodeTiled or refused the tensor map */
 #define LAB200_ERR_ALIGN 6       /* a pointer is not 16-byte aligned */
+#define LAB200_ERR_SCRATCH_LIMIT 7 /* lab200_la2_fwd_static: the problem needs more than the built-in scratch */
+
+/* Size of the scratch array built into the library for lab200_la2_fwd_static. */
+#define LAB200_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
 #define LAB200_ERR_WAIT_INPUT 101 /* device side: a bounded barrier wait ran out (see lab200_read_status) */
 #define LAB200_ERR_WAIT_MMA1 102
 #define LAB200_ERR_WAIT_MMA2 103
@@ -90,6 +94,27 @@ int lab200_la_generic(const void* a, const void* bm, const void* c, const float*
 int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slopes, void* o,
                    void* workspace, size_t workspace_bytes, int b, int h, int n, int d, int e,
                    int chunks, int dtype, void* stream);
+
+/*
+ * lab200_la2_fwd for callers that cannot hand over a workspace. It has no counterpart in the reference.
+ *
+ * Who needs it: code that runs where device memory cannot be obtained at call time -- a plugin whose host
+ * passes it only the input and output buffers and offers no allocator, or a serving loop that must not call
+ * cudaMalloc because that call synchronises the whole device and may fail once memory is fully committed to
+ * other tenants. For them the scratch (status word + per-chunk states) is a fixed array of
+ * LAB200_STATIC_SCRATCH_BYTES (16 MiB) inside the library's device image. The price: every GPU that loads the
+ * library carries those 16 MiB until the process exits, whether or not this entry point is ever called.
+ *
+ * Behaviour: same result as lab200_la2_fwd with the same `chunks`. The call allocates and frees nothing.
+ * Problems whose workspace (lab200_la_workspace_bytes(b*h, n, d, e, chunks)) exceeds the array are refused with
+ * LAB200_ERR_SCRATCH_LIMIT before anything is enqueued; pass chunks = 1 to need only the status word.
+ * The first call on each device looks up the array's device address (a host-side runtime query, done once per
+ * device with that device current); make that first call outside any stream capture.
+ * All calls on a device share the one array: calls whose GPU execution may overlap (different streams, or
+ * different host threads on different streams) race on it and must be serialised by the caller.
+ */
+int lab200_la2_fwd_static(const void* q, const void* k, const void* v, const float* slopes, void* o,
+                          int b, int h, int n, int d, int e, int chunks, int dtype, void* stream);
 
 /* dq, dk, dv = LightningAttention2.backward(do): lightning_attn2.py:437-504 and
  * lightning_attn2_no_decay.py:403-468. Workspace size: lab200_la_workspace_bytes(b*h, n, max(d,e), max(d,e), chunks). */

@@ -305,6 +305,37 @@ int srms_entry(bool fwd, const void* x, const void* dy, void* out, float* rstd, 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch for lab200_la2_fwd_static: lives in the library's device image, so it exists on every
+// GPU that loads the library, from load until the process ends.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[LAB200_STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+void* g_static_scratch_addr[MAX_DEVICES] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of g_static_scratch on the current device. In host code the array's name is only a handle
+// for the runtime, not an address a kernel could use; cudaGetSymbolAddress translates it, once per device.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    cudaGetLastError();
+    return LAB200_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return LAB200_ERR_CUDA;
+    }
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return LAB200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -327,6 +358,7 @@ const char* lab200_error_string(int code) {
     case LAB200_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
     case LAB200_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or refused the tensor map";
     case LAB200_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case LAB200_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the library's built-in 16 MiB";
     case LAB200_ERR_WAIT_INPUT: return "device: bounded wait for TMA input ran out";
     case LAB200_ERR_WAIT_MMA1: return "device: bounded wait for the first MMA group ran out";
     case LAB200_ERR_WAIT_MMA2: return "device: bounded wait for the second MMA group ran out";
@@ -366,6 +398,25 @@ int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slo
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
   return la_generic_impl(q, k, v, slopes, o, nullptr, nullptr, workspace, workspace_bytes, b * h, h, n, d, e, 0, 0,
                          chunks, dtype, st);
+}
+
+int lab200_la2_fwd_static(const void* q, const void* k, const void* v, const float* slopes, void* o, int b, int h,
+                          int n, int d, int e, int chunks, int dtype, void* stream) {
+  if (b < 1 || h < 1 || b > 65535 / h) return LAB200_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the scratch pointer is not known yet; validate everything else against a stand-in aligned address
+  int rc = la_validate(q, k, v, o, nullptr, nullptr, reinterpret_cast<const void*>(uintptr_t{256}), b * h, h, n, d, e, 0,
+                       dtype);
+  if (rc != LAB200_OK) return rc;
+  if (lab200_la_workspace_bytes(b * h, n, d, e, chunks) > static_cast<size_t>(LAB200_STATIC_SCRATCH_BYTES))
+    return LAB200_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  if ((rc = static_scratch_address(&scratch)) != LAB200_OK) return rc;
+  // the array keeps whatever the previous call left: the status word must start at zero; the chunk states
+  // need no clearing because the state kernel writes every slot that the scan reads
+  if ((rc = reset_status(scratch, LAB200_STATIC_SCRATCH_BYTES, st)) != LAB200_OK) return rc;
+  return la_generic_impl(q, k, v, slopes, o, nullptr, nullptr, scratch, LAB200_STATIC_SCRATCH_BYTES, b * h, h, n, d, e,
+                         0, 0, chunks, dtype, st);
 }
 
 int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dq,
