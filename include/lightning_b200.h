@@ -53,11 +53,14 @@ int lab200_version(void);
  * all streams). Bookkeeping for benchmarks; no counterpart in the reference. */
 long long lab200_launch_count(void);
 
-/* Profiling aid, off by default: while `device_buffer` is non-NULL, CTA (0,0,0) of every attention
- * block kernel writes clock64() at six points of each of its first `blocks` 128-token blocks into
- * device_buffer[block * 6 + point] (points: block start, inputs landed, first MMA group done, masked
- * tile stored, second MMA group done, epilogue done). Pass NULL to switch it off. No counterpart
- * in the reference. */
+/* Profiling aid, off by default: while `device_buffer` is non-NULL, the CTA that handles (batch*head 0,
+ * slice 0, chunk 0) of every attention block kernel writes clock64() stamps for each of its first `blocks`
+ * 128-token blocks into device_buffer[block * 16 + slot]. Slots 0-5 (serial kernel): block start, inputs landed,
+ * first MMA group done, masked tile stored, second MMA group done, epilogue done. Slots 0-11 (pipelined kernel):
+ * MMA issuer (0 inputs landed, 1 S and X issued, 2 P ready, 3 PC and D issued), mask group (4 S ready, 5 P stored,
+ * 6 Bm scaled), state/output group (7 PC and D done, 8 D consumed, 9 state published, 10 accumulators released,
+ * 11 output rows stored). The buffer must hold blocks * 16 64-bit words. Pass NULL to switch it off. No
+ * counterpart in the reference. */
 void lab200_la_debug_trace(long long* device_buffer, int blocks);
 
 /* Static, human-readable text for an error code. */

@@ -5,7 +5,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "liblightning_b200.so")
+# LIGHTNING_B200_LIB overrides the in-tree library (e.g. to try an experimental build).
+LIB_PATH = os.environ.get("LIGHTNING_B200_LIB") or os.path.join(_HERE, "liblightning_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}

@@ -11,12 +11,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "liblightning_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 SOURCES = [os.path.join(HERE, "csrc", "capi.cu")]
-HEADERS = [
-    os.path.join(HERE, "csrc", "ptx_sm100.cuh"),
-    os.path.join(HERE, "csrc", "la_kernels.cuh"),
-    os.path.join(HERE, "csrc", "srmsnorm_kernels.cuh"),
-    os.path.join(HERE, "..", "include", "lightning_b200.h"),
-]
+import glob
+
+HEADERS = sorted(glob.glob(os.path.join(HERE, "csrc", "*.cuh"))) + [os.path.join(HERE, "..", "include", "lightning_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

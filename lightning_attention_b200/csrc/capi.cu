@@ -4,12 +4,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
 
 #include "../../include/lightning_b200.h"
 #include "la_kernels.cuh"
+#include "la_pipe_kernel.cuh"
 #include "srmsnorm_kernels.cuh"
 
 using namespace lab200;
@@ -126,8 +128,64 @@ int launch_tiled(int nks, int nvs, const CUtensorMap& tA, const CUtensorMap& tB,
   return LAB200_ERR_SHAPE;
 }
 
+// ---- pipelined kernel (dk <= 128) ---------------------------------------------------------------
+int smem_bytes_pipe(int nks, int nvs, int mode) {
+  const int slab = LA_SLAB_BYTES;
+  int b = 2 * nks * slab + 4 * slab;
+  if (mode == 0) b += 2 * nks * slab + nks * nvs * 64 * 128;
+  return b + 2 * LAP_NUM_BARS * 8 + 16 + 512 + 1024;  // barriers, flags, decay table, alignment slack
+}
+
+template <int NKS, int NVS, int MODE, int FMT>
+int launch_pipe_one(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const CUtensorMap& tO,
+                    const LaParams& p, dim3 grid, int smem, cudaStream_t st) {
+  auto kern = la_pipe_kernel<NKS, NVS, MODE, FMT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return LAB200_ERR_CUDA;
+  }
+  kern<<<grid, LAP_THREADS, smem, st>>>(tA, tB, tC, tO, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
+}
+
+template <int MODE, int FMT>
+int launch_pipe(int nks, int nvs, const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
+                const CUtensorMap& tO, const LaParams& p, dim3 grid, int smem, cudaStream_t st) {
+#define LAB200_CASE(K, V) \
+  if (nks == K && nvs == V) return launch_pipe_one<K, V, MODE, FMT>(tA, tB, tC, tO, p, grid, smem, st);
+  LAB200_CASE(1, 1)
+  LAB200_CASE(1, 2)
+  LAB200_CASE(2, 1)
+  LAB200_CASE(2, 2)
+#undef LAB200_CASE
+  return LAB200_ERR_SHAPE;
+}
+
+// LIGHTNING_B200_SERIAL=1 in the environment selects the serial block kernel for every shape (A/B comparisons).
+bool use_pipelined_kernel() {
+  static const bool on = [] {
+    const char* e = getenv("LIGHTNING_B200_SERIAL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
 int launch_la(int mode, int dtype, const Tiling& t, const CUtensorMap& tA, const CUtensorMap& tB,
-              const CUtensorMap& tC, LaParams p, int nchunks_grid, int bh, cudaStream_t st) {
+              const CUtensorMap& tC, const CUtensorMap& tO, LaParams p, int nchunks_grid, int bh, cudaStream_t st) {
+  if (t.nks <= 2 && use_pipelined_kernel()) {
+    const int smem = smem_bytes_pipe(t.nks, t.nvs, mode);
+    if (smem <= SMEM_LIMIT) {
+      p.nstage = 2;
+      const dim3 grid(t.nslices, nchunks_grid, bh);
+      if (mode == 0) {
+        return dtype == LAB200_BF16 ? launch_pipe<0, 1>(t.nks, t.nvs, tA, tB, tC, tO, p, grid, smem, st)
+                                    : launch_pipe<0, 0>(t.nks, t.nvs, tA, tB, tC, tO, p, grid, smem, st);
+      }
+      return dtype == LAB200_BF16 ? launch_pipe<1, 1>(t.nks, t.nvs, tA, tB, tC, tO, p, grid, smem, st)
+                                  : launch_pipe<1, 0>(t.nks, t.nvs, tA, tB, tC, tO, p, grid, smem, st);
+    }
+  }
   int nstage = 2;
   int smem = smem_bytes(t.nks, t.nvs, mode, nstage);
   if (smem > SMEM_LIMIT) {
@@ -168,13 +226,15 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   const size_t need = WS_HEADER + (nchunks > 1 ? static_cast<size_t>(bh) * nchunks * dv * dk * sizeof(float) : 0);
   if (!workspace || workspace_bytes < need) return LAB200_ERR_WORKSPACE;
 
-  CUtensorMap tA, tB, tC;
+  CUtensorMap tA, tB, tC, tO;
   if ((rc = make_tmap(&tB, bm, bh, n, dk, dtype)) != LAB200_OK) return rc;
   if ((rc = make_tmap(&tC, c, bh, n, dv, dtype)) != LAB200_OK) return rc;
   if (state_only) {
     tA = tB;
-  } else if ((rc = make_tmap(&tA, a, bh, n, dk, dtype)) != LAB200_OK) {
-    return rc;
+    tO = tC;
+  } else {
+    if ((rc = make_tmap(&tA, a, bh, n, dk, dtype)) != LAB200_OK) return rc;
+    if ((rc = make_tmap(&tO, out, bh, n, dv, dtype)) != LAB200_OK) return rc;  // output tiles leave through TMA stores
   }
 
   LaParams p;
@@ -195,7 +255,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
     p.state_slots = 1;
     p.state_in = state_in;
     p.state_out = state_out;
-    return launch_la(state_only ? 1 : 0, dtype, t, tA, tB, tC, p, 1, bh, st);
+    return launch_la(state_only ? 1 : 0, dtype, t, tA, tB, tC, tO, p, 1, bh, st);
   }
 
   // three phases: local chunk states -> decayed scan -> block loop per chunk with its incoming state
@@ -206,7 +266,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   p.state_in = nullptr;
   p.state_out = states;
   p.chunk0 = (skip_last && reverse) ? 1 : 0;
-  if ((rc = launch_la(1, dtype, t, tB, tB, tC, p, nchunks - skip_last, bh, st)) != LAB200_OK) return rc;
+  if ((rc = launch_la(1, dtype, t, tB, tB, tC, tC, p, nchunks - skip_last, bh, st)) != LAB200_OK) return rc;
 
   const int elems = dv * dk;
   const long long total = static_cast<long long>(bh) * elems;
@@ -221,7 +281,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   p.chunk0 = 0;
   p.state_in = states;
   p.state_out = nullptr;
-  return launch_la(0, dtype, t, tA, tB, tC, p, nchunks, bh, st);
+  return launch_la(0, dtype, t, tA, tB, tC, tO, p, nchunks, bh, st);
 }
 
 // Argument checks that need no CUDA call; run before anything is enqueued.

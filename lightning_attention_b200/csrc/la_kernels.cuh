@@ -34,11 +34,16 @@
 #include <cuda_fp16.h>
 #include "ptx_sm100.cuh"
 
+#ifndef LA_P_IN_TMEM
+#define LA_P_IN_TMEM 0
+#endif
+
 namespace lab200 {
 
 constexpr int LA_BLOCK = 128;        // tokens per block
 constexpr int LA_SLAB_BYTES = 16384; // 128 rows x 128 bytes
 constexpr int LA_THREADS = 256;
+constexpr int LA_TRACE_SLOTS = 16;    // clock stamps per block in the optional trace buffer
 
 enum LaError : int {
   LA_OK = 0,
@@ -61,7 +66,7 @@ struct LaParams {
   int reverse;
   int nstage;              // 1 or 2 shared-memory stages for the Bm and C tiles
   long long wait_budget;   // clock cycles after which a barrier wait gives up
-  long long* trace;        // optional: CTA (0,0,0) records clock64() at 6 points per block here
+  long long* trace;        // optional: CTA (0,0,0) records clock64() stamps here, LA_TRACE_SLOTS per block
   int trace_blocks;        // capacity of `trace` in blocks
 };
 
@@ -73,6 +78,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   } else {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+// packed multiply of two 16-bit pairs (rounds once per element, in the 16-bit format)
+template <int FMT>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+  if constexpr (FMT == 1) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  } else {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
   }
 }
 template <int FMT>
@@ -225,7 +241,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   int failed = 0;
   const bool tracing = (p.trace != nullptr) && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#define LA_TRACE(slot) if (tracing && it < p.trace_blocks) p.trace[it * 6 + (slot)] = clock64();
+#define LA_TRACE(slot) if (tracing && it < p.trace_blocks) p.trace[it * LA_TRACE_SLOTS + (slot)] = clock64();
 
   for (int it = 0; it < nb; ++it) {
     LA_TRACE(0)
@@ -274,6 +290,41 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         issue_A(nxt);
         if (nstage == 2) issue_BC(nxt, stage ^ 1);
       }
+#if LA_P_IN_TMEM
+      {
+        // experiment: P goes back into TMEM (aliasing the first 64 columns of S) as the A operand of P C
+        uint32_t v[2][32];
+        bool deadt[2];
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c0 = hf * 64 + cc * 32;
+          deadt[cc] = reverse ? (c0 + 31 < q * 32) : (c0 > q * 32 + 31);
+          if (!deadt[cc]) tmem_ld32(tmem + lanebase + T_S + c0, v[cc]);
+        }
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        __syncthreads();  // every warp holds its part of S in registers before anyone overwrites it
+        tc_fence_after_sync();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c0 = hf * 64 + cc * 32;
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float f0 = 0.f, f1 = 0.f;
+            if (!deadt[cc]) {
+              const int d0 = reverse ? (c0 + i - r) : (r - c0 - i);
+              const int d1 = reverse ? (d0 + 1) : (d0 - 1);
+              if (d0 >= 0) f0 = __uint_as_float(v[cc][i]) * decay_tab[d0];
+              if (d1 >= 0) f1 = __uint_as_float(v[cc][i + 1]) * decay_tab[d1];
+            }
+            pk[i >> 1] = pack2<FMT>(f0, f1);
+          }
+          tmem_st16(tmem + lanebase + T_S + (c0 >> 1), pk);
+        }
+        tmem_wait_st();
+      }
+#else
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c0 = hf * 64 + cc * 32;
@@ -302,6 +353,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           st_shared_v4(addr, pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
         }
       }
+#endif
     } else {
       if (tid == 0 && has_next && nstage == 2) issue_BC(nxt, stage ^ 1);
     }
@@ -333,8 +385,12 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (MODE == 0) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
+#if LA_P_IN_TMEM
+          umma_f16_ts(tmem + T_OI, tmem + T_S + kk * 8, smem_desc_sw128(sCs + kk * 2048, SLAB), IDESC_PC, kk > 0);
+#else
           umma_f16(tmem + T_OI, smem_desc_sw128(sP + (kk >> 2) * SLAB + (kk & 3) * 32, 16),
                    smem_desc_sw128(sCs + kk * 2048, SLAB), IDESC_PC, kk > 0);
+#endif
         }
       }
 #pragma unroll
