@@ -33,7 +33,7 @@ ALG_BYTES_PER_UNIT = 2816
 ALG_FLOP_PER_UNIT = 344064
 LA_LAUNCHES_PER_STEP = 4  # forward, dq, dk, dv: four launches of the same block kernel
 # DRAM bytes (read + write) per launch of la_chunk_kernel measured with ncu; see profiles/. None = not captured yet.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 4 * 1048.7e6  # n=8192 capture (1048.7 MB) scaled x4: traffic is linear in n
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -361,7 +361,7 @@ def main():
         launch_ms = (fwd_ms + bwd_ms) / LA_LAUNCHES_PER_STEP
         achieved = ALG_BYTES_PER_UNIT * units / LA_LAUNCHES_PER_STEP / (launch_ms * 1e-3) / 1e9
         roofline = {
-            "bound": "hbm", "kernel": "la_chunk_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+            "bound": "hbm", "kernel": "la_pipe_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
             "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
             "launch_ms": launch_ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
             "alg_tflops": ALG_FLOP_PER_UNIT * units / ((fwd_ms + bwd_ms) * 1e-3) / 1e12,
