@@ -60,6 +60,17 @@ def test_reference_shape_list_bf16(cuda_lib, b, h, n, d, e):
     compare_with_torch_reference(q, k, v, do, s, got, True, f"decay{(b, h, n, d, e)}")
 
 
+@pytest.mark.parametrize("b,h,n,d,e", [REF_SHAPES[i] for i in (0, 3, 6, 7, 11, 14, 17)])
+def test_reference_shape_list_fp16(cuda_lib, b, h, n, d, e):
+    """The reference's second dtype (tests/ops/test_lightning2.py:35), subset of its shape list. fp16 rounds finer than
+    bf16, so the same tolerance applies with room to spare; the running state is carried in fp32 and only its
+    tensor-core copy is fp16, which randn/10 inputs keep far from the fp16 range limit."""
+    q, k, v, do = make_inputs(b, h, n, d, e, torch.float16, 0.1)
+    s = la._build_slope_tensor(h).to(DEV)
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2(a, b_, c, s), q, k, v, do)
+    compare_with_torch_reference(q, k, v, do, s, got, True, f"fp16{(b, h, n, d, e)}")
+
+
 @pytest.mark.parametrize("b,h,n,d,e", [REF_SHAPES[i] for i in (0, 3, 6, 14, 15, 17)])
 def test_reference_shape_list_no_decay_bf16(cuda_lib, b, h, n, d, e):
     """tests/ops/test_lightning2_no_decay.py:31-56 (s=None), subset of its shape list."""
