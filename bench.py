@@ -165,6 +165,76 @@ def run_reference(args, rank):
     }), flush=True)
 
 
+# The reference's published tables (ms; hardware not stated): README.md:58-76 and benchmarks/README.md:6-24,52-69.
+REF_LIGHTNING2_FWD = {512: 0.351540, 1024: 0.585876, 2048: 1.134238, 4096: 2.240815, 8192: 4.414397, 16384: 8.832678, 32768: 17.661427}
+REF_LIGHTNING2_BWD = {512: 1.169621, 1024: 2.334296, 2048: 4.657026, 4096: 9.307817, 8192: 18.617611, 16384: 37.212578, 32768: 74.594788}
+REF_NODECAY_FWD = {512: 0.416118, 1024: 0.758793, 2048: 1.477481, 4096: 2.949107, 8192: 6.018426, 16384: 11.795692, 32768: 23.883759}
+REF_NODECAY_BWD = {512: 1.378255, 1024: 2.653988, 2048: 5.504418, 4096: 11.009040, 8192: 21.968288, 16384: 36.816639, 32768: 73.657219}
+REF_SRMS_FWD = {512: 0.040659, 1024: 0.068261, 2048: 0.124653, 4096: 0.236823, 8192: 0.460920, 16384: 0.912446, 32768: 1.818576}
+REF_SRMS_BWD = {512: 0.102669, 1024: 0.186009, 2048: 0.354364, 4096: 0.690570, 8192: 1.363543, 16384: 2.711788, 32768: 5.410873}
+
+
+def run_sweep():
+    """The reference's two benchmark tables on one GPU, same shapes and timing style (warm-up, median of repeated
+    CUDA-event timings, L2 flushed between repetitions): benchmarks/benchmark_lightning2.py:56-118 (b4 h32 d=e=128 bf16,
+    fwd and bwd separately, with and without decay) and benchmarks/benchmark_srmsnorm.py (b12, dim 2048 bf16)."""
+    import torch
+
+    import lightning_attention_b200 as la
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=15, warm=5):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b_.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b_))
+        return statistics.median(ts)
+
+    torch.manual_seed(SEED)
+    s = la._build_slope_tensor(H).to(dev)
+    for n in (512, 1024, 2048, 4096, 8192, 16384, 32768):
+        q, k, v = (torch.randn((B, H, n, D), device=dev, dtype=torch.bfloat16).requires_grad_() for _ in range(3))
+        do = torch.randn((B, H, n, D), device=dev, dtype=torch.bfloat16)
+        for name, fn, ref_f, ref_b in (("lightning2", lambda: la.lightning_attn2(q, k, v, s), REF_LIGHTNING2_FWD, REF_LIGHTNING2_BWD),
+                                       ("lightning2_no_decay", lambda: la.lightning_attn2_no_decay(q, k, v), REF_NODECAY_FWD, REF_NODECAY_BWD)):
+            fwd = timed(fn)
+            o = fn()
+
+            def bwd_fn():
+                q.grad = k.grad = v.grad = None
+                o.backward(do, retain_graph=True)
+
+            bwd = timed(bwd_fn)
+            units = B * H * n
+            print(json.dumps({"table": name, "n": n, "fwd_ms": fwd, "bwd_ms": bwd, "ref_fwd_ms": ref_f[n], "ref_bwd_ms": ref_b[n],
+                              "tokens_per_s_fwd_bwd": B * n / ((fwd + bwd) * 1e-3),
+                              "hbm_frac_of_measured": ALG_BYTES_PER_UNIT * units / ((fwd + bwd) * 1e-3) / 1e9 / load_peaks()[0]}), flush=True)
+        del q, k, v, do
+    for n in (512, 1024, 2048, 4096, 8192, 16384, 32768):
+        x = torch.randn((12, n, 2048), device=dev, dtype=torch.bfloat16).requires_grad_()
+        dy = torch.randn((12, n, 2048), device=dev, dtype=torch.bfloat16)
+        norm = la.SimpleRMSNorm(2048)
+        fwd = timed(lambda: norm(x))
+        y = norm(x)
+
+        def bwd_fn():
+            x.grad = None
+            y.backward(dy, retain_graph=True)
+
+        bwd = timed(bwd_fn)
+        elems = 12 * n * 2048
+        print(json.dumps({"table": "srmsnorm", "n": n, "fwd_ms": fwd, "bwd_ms": bwd, "ref_fwd_ms": REF_SRMS_FWD[n], "ref_bwd_ms": REF_SRMS_BWD[n],
+                          "fwd_gbs": 4.0 * elems / fwd / 1e6, "bwd_gbs": 6.0 * elems / bwd / 1e6}), flush=True)
+
+
 def main():
     global N_TOK
     ap = argparse.ArgumentParser()
@@ -176,6 +246,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--n", type=int, default=N_TOK, help="sequence length (default: the benchmark's largest point)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="instead of the single bench line, print one JSON line per point of the reference's benchmark "
+                         "tables (Lightning2 / NoDecay fwd and bwd over n; SRMSNorm fwd and bwd over n) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     N_TOK = args.n
@@ -186,6 +259,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.sweep:
+        run_sweep()
         return
 
     import torch
