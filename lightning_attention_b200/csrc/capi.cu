@@ -12,6 +12,7 @@
 #include "../../include/lightning_b200.h"
 #include "la_kernels.cuh"
 #include "la_pipe_kernel.cuh"
+#include "la_dkdv_kernel.cuh"
 #include "srmsnorm_kernels.cuh"
 
 using namespace lab200;
@@ -284,6 +285,73 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   return launch_la(0, dtype, t, tA, tB, tC, tO, p, nchunks, bh, st);
 }
 
+// ---- fused dk + dv (one reverse sweep) -----------------------------------------------------------------
+int smem_bytes_dkdv(int ne) {
+  return 12 * LA_SLAB_BYTES + ne * LA_SLAB_BYTES + 2 * LDK_NUM_BARS * 8 + 16 + 512 + 1024;
+}
+
+template <int ND, int NE, int FMT>
+int launch_dkdv_one(const CUtensorMap (&tm)[6], const LaDkdvParams& p, dim3 grid, int smem, cudaStream_t st) {
+  auto kern = la_dkdv_kernel<ND, NE, FMT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return LAB200_ERR_CUDA;
+  }
+  kern<<<grid, LAP_THREADS, smem, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
+}
+
+// LIGHTNING_B200_NO_FUSED_BWD=1 makes the backward pass use three launches of the generic kernel (A/B comparisons).
+bool use_fused_dkdv() {
+  static const bool on = [] {
+    const char* e = getenv("LIGHTNING_B200_NO_FUSED_BWD");
+    return !(e && e[0] == '1');
+  }();
+  return on && use_pipelined_kernel();
+}
+
+// dk and dv in one launch; only the unchunked case (one CTA per (batch, head) pair). Returns LAB200_ERR_SHAPE if the
+// shape is not covered, in which case the caller falls back to two generic launches.
+int la_dkdv_impl(const void* q, const void* k, const void* v, const void* dout, const float* slopes, void* dk, void* dv,
+                 void* workspace, int bh, int h, int n, int d, int e, int dtype, cudaStream_t st) {
+  if (d > 128 || e > 128 || (d % 16) || (e % 16) || d < 16 || e < 16) return LAB200_ERR_SHAPE;
+  const int nd = (d + 63) / 64, ne = (e + 63) / 64;
+  const int smem = smem_bytes_dkdv(ne);
+  if (smem > SMEM_LIMIT) return LAB200_ERR_SHAPE;
+  CUtensorMap tm[6];
+  int rc;
+  if ((rc = make_tmap(&tm[0], q, bh, n, d, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[1], k, bh, n, d, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[2], v, bh, n, e, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[3], dout, bh, n, e, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[4], dk, bh, n, d, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[5], dv, bh, n, e, dtype)) != LAB200_OK) return rc;
+  LaDkdvParams p;
+  p.slopes = slopes;
+  p.state_in = nullptr;
+  p.state_out = nullptr;
+  p.status = static_cast<int*>(workspace);
+  p.n = n; p.h = h; p.d = d; p.e = e;
+  p.nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
+  p.blocks_per_chunk = p.nblocks;
+  p.chunk0 = 0;
+  p.state_slots = 1;
+  p.wait_budget = WAIT_BUDGET;
+  p.trace = g_trace.load(std::memory_order_relaxed);
+  p.trace_blocks = g_trace_blocks.load(std::memory_order_relaxed);
+  const dim3 grid(1, 1, bh);
+  const bool bf = (dtype == LAB200_BF16);
+#define LAB200_CASE(D_, E_) \
+  if (nd == D_ && ne == E_) return bf ? launch_dkdv_one<D_, E_, 1>(tm, p, grid, smem, st) : launch_dkdv_one<D_, E_, 0>(tm, p, grid, smem, st);
+  LAB200_CASE(1, 1)
+  LAB200_CASE(1, 2)
+  LAB200_CASE(2, 1)
+  LAB200_CASE(2, 2)
+#undef LAB200_CASE
+  return LAB200_ERR_SHAPE;
+}
+
 // Argument checks that need no CUDA call; run before anything is enqueued.
 int la_validate(const void* a, const void* bm, const void* c, const void* out, const float* state_in,
                 const float* state_out, const void* workspace, int bh, int h, int n, int dk, int dv, int state_only,
@@ -494,11 +562,20 @@ int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slo
   rc = la_generic_impl(dout, v, k, slopes, dq, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, e, d, 0, 0,
                        chunks, dtype, st);
   if (rc != LAB200_OK) return rc;
-  // dk_t = sum_{j>=t} lambda^(j-t) (v_t . do_j) q_j
+  // dk_t = sum_{j>=t} lambda^(j-t) (v_t . do_j) q_j  and  dv_t = sum_{j>=t} lambda^(j-t) (k_t . q_j) do_j:
+  // one fused reverse sweep when every (batch, head) pair gets one CTA, else two launches of the generic kernel
+  {
+    const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
+    int nchunks = chunks > 0 ? chunks : plan_chunks(bh, n, e, d);
+    if (nchunks > nblocks) nchunks = nblocks;
+    if (nchunks == 1 && use_fused_dkdv()) {
+      rc = la_dkdv_impl(q, k, v, dout, slopes, dk, dv, workspace, bh, h, n, d, e, dtype, st);
+      if (rc != LAB200_ERR_SHAPE) return rc;
+    }
+  }
   rc = la_generic_impl(v, dout, q, slopes, dk, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, e, d, 1, 0,
                        chunks, dtype, st);
   if (rc != LAB200_OK) return rc;
-  // dv_t = sum_{j>=t} lambda^(j-t) (k_t . q_j) do_j
   return la_generic_impl(k, q, dout, slopes, dv, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, d, e, 1, 0,
                          chunks, dtype, st);
 }
