@@ -31,7 +31,7 @@ SEED = 2024
 # (read q,k,v / write o; read q,k,v,do / write dq,dk,dv) and flops with the reference's 64-token blocks.
 ALG_BYTES_PER_UNIT = 2816
 ALG_FLOP_PER_UNIT = 344064
-LA_LAUNCHES_PER_STEP = 4  # forward, dq, dk, dv: four launches of the same block kernel
+LA_LAUNCHES_PER_STEP = 4  # generic-product equivalents per step: o, dq, dk, dv (dk and dv share one fused launch)
 # DRAM bytes (read + write) per launch of la_chunk_kernel measured with ncu; see profiles/. None = not captured yet.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 4 * 1048.7e6  # n=8192 capture (1048.7 MB) scaled x4: traffic is linear in n
 FALLBACK_HBM_GBS = 6650.0

@@ -125,6 +125,14 @@ int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slo
                    void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h,
                    int n, int d, int e, int chunks, int dtype, void* stream);
 
+/* dk and dv of the same backward pass in ONE reverse-time sweep that reads q, k, v, do once (6 tensor passes instead
+ * of the 8 that two generic launches move); one CTA per (batch, head) pair, d, e <= 128. Same results as the dk, dv of
+ * lab200_la2_bwd. Stands in for the dk/dv halves of _bwd_intra_kernel (lightning_attn2.py:156-162) and of the
+ * reverse sweep of _bwd_inter_kernel (:335-395). Workspace: 256 bytes (status word only). */
+int lab200_la2_dkdv(const void* q, const void* k, const void* v, const float* slopes, const void* dout,
+                    void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h, int n,
+                    int d, int e, int dtype, void* stream);
+
 /* Synchronises `stream` and returns the device-side status word of the last attention call that
  * used `workspace` (0, or one of LAB200_ERR_WAIT_*). Negative: the copy itself failed. */
 int lab200_read_status(const void* workspace, void* stream);

@@ -43,6 +43,8 @@ def lib():
         L.lab200_la2_fwd.argtypes = [vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, vp]
         L.lab200_la2_fwd_static.restype = i
         L.lab200_la2_fwd_static.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, vp]
+        L.lab200_la2_dkdv.restype = i
+        L.lab200_la2_dkdv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, vp]
         L.lab200_la2_bwd.restype = i
         L.lab200_la2_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, vp]
         L.lab200_read_status.restype = i
@@ -57,7 +59,7 @@ def lib():
 
 EXPORTS = [
     "lab200_version", "lab200_launch_count", "lab200_la_debug_trace", "lab200_error_string", "lab200_la_plan_chunks", "lab200_la_workspace_bytes",
-    "lab200_la_generic", "lab200_la2_fwd", "lab200_la2_fwd_static", "lab200_la2_bwd", "lab200_read_status",
+    "lab200_la_generic", "lab200_la2_fwd", "lab200_la2_fwd_static", "lab200_la2_bwd", "lab200_la2_dkdv", "lab200_read_status",
     "lab200_srmsnorm_fwd", "lab200_srmsnorm_bwd",
 ]
 

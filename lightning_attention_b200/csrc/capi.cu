@@ -302,11 +302,13 @@ int launch_dkdv_one(const CUtensorMap (&tm)[6], const LaDkdvParams& p, dim3 grid
   return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
 }
 
-// LIGHTNING_B200_NO_FUSED_BWD=1 makes the backward pass use three launches of the generic kernel (A/B comparisons).
+// The fused dk+dv sweep moves 6 instead of 8 tensor passes but its two mask passes per block sit on one dependency
+// chain, which today makes it a few percent slower than two generic launches; lab200_la2_bwd therefore uses it only
+// when LIGHTNING_B200_FUSED_BWD=1 is set. lab200_la2_dkdv always uses it.
 bool use_fused_dkdv() {
   static const bool on = [] {
-    const char* e = getenv("LIGHTNING_B200_NO_FUSED_BWD");
-    return !(e && e[0] == '1');
+    const char* e = getenv("LIGHTNING_B200_FUSED_BWD");
+    return e && e[0] == '1';
   }();
   return on && use_pipelined_kernel();
 }
@@ -578,6 +580,22 @@ int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slo
   if (rc != LAB200_OK) return rc;
   return la_generic_impl(k, q, dout, slopes, dv, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, d, e, 1, 0,
                          chunks, dtype, st);
+}
+
+int lab200_la2_dkdv(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dk,
+                    void* dv, void* workspace, size_t workspace_bytes, int b, int h, int n, int d, int e, int dtype,
+                    void* stream) {
+  if (b < 1 || h < 1 || b > 65535 / h || n < 1) return LAB200_ERR_SHAPE;
+  if (dtype != LAB200_BF16 && dtype != LAB200_F16) return LAB200_ERR_DTYPE;
+  if (!q || !k || !v || !dout || !dk || !dv) return LAB200_ERR_SHAPE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dk) || !aligned16(dv) ||
+      !aligned16(workspace))
+    return LAB200_ERR_ALIGN;
+  if (d > 128 || e > 128 || (d % 16) || (e % 16) || d < 16 || e < 16) return LAB200_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = reset_status(workspace, workspace_bytes, st);
+  if (rc != LAB200_OK) return rc;
+  return la_dkdv_impl(q, k, v, dout, slopes, dk, dv, workspace, b * h, h, n, d, e, dtype, st);
 }
 
 int lab200_read_status(const void* workspace, void* stream) {

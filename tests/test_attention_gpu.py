@@ -288,3 +288,29 @@ def test_sequence_parallel_math_on_one_gpu(cuda_lib, scale):
     ref = run_fwd_bwd(lambda a, b_, c: torch_la_reference(a, b_, c, s), qr, kr, vr, do.float())
     for x, r_, name in zip(got, ref, ("o", "dq", "dk", "dv")):
         assert_parity(x, r_, f"sp-emulated:{name}", False)
+
+
+@pytest.mark.parametrize("b,h,n,d,e,decay", [(2, 4, 1024, 128, 128, True), (1, 3, 513, 128, 64, True), (2, 2, 300, 64, 128, True),
+                                             (1, 2, 77, 32, 16, True), (1, 4, 2048, 128, 128, False), (1, 2, 128, 16, 16, True)])
+def test_fused_dk_dv_sweep(cuda_lib, b, h, n, d, e, decay):
+    """lab200_la2_dkdv (dk and dv in one reverse sweep) against the fp32 reference gradients and against the dk, dv that
+    lab200_la2_bwd produces with the generic kernel."""
+    q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(h).to(DEV) if decay else None
+    sl = None if s is None else s.reshape(-1).contiguous()
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    ws = torch.empty(256, dtype=torch.uint8, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = cuda_lib.lab200_la2_dkdv(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), do.data_ptr(), dk.data_ptr(),
+                                  dv.data_ptr(), ws.data_ptr(), 256, b, h, n, d, e, _lib.BF16, stream)
+    assert rc == 0, cuda_lib.lab200_error_string(rc)
+    assert cuda_lib.lab200_read_status(ws.data_ptr(), stream) == 0
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    _, _, rdk, rdv = run_fwd_bwd(lambda a, b_, c: torch_la_reference(a, b_, c, s), qr, kr, vr, do.float())
+    assert_parity(dk, rdk, "fused:dk", False)
+    assert_parity(dv, rdv, "fused:dv", False)
+    fn = (lambda a, b_, c: la.lightning_attn2(a, b_, c, s)) if decay else (lambda a, b_, c: la.lightning_attn2_no_decay(a, b_, c))
+    _, _, gdk, gdv = run_fwd_bwd(fn, q, k, v, do)
+    assert_parity(dk, gdk.float(), "fused-vs-generic:dk", False)
+    assert_parity(dv, gdv.float(), "fused-vs-generic:dv", False)
