@@ -143,7 +143,7 @@ def host_threads():
         return os.cpu_count() or 1
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, emit):
     if rank != 0:
         return
     pairs = host_threads()
@@ -154,7 +154,7 @@ def run_reference(args, rank):
     value = B * N_TOK * (pairs / float(B * H)) / dt
     sample = (f"{pairs} of {B * H} (batch, head) pairs at n={N_TOK}, d=e={D}, fp32 numpy block recurrences, fwd+bwd, "
               "one pair per host thread, scaled to the full step")
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": "lightning2_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -162,7 +162,7 @@ def run_reference(args, rank):
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": host_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }), flush=True)
+    }))
 
 
 # The reference's published tables (ms; hardware not stated): README.md:58-76 and benchmarks/README.md:6-24,52-69.
@@ -174,7 +174,7 @@ REF_SRMS_FWD = {512: 0.040659, 1024: 0.068261, 2048: 0.124653, 4096: 0.236823, 8
 REF_SRMS_BWD = {512: 0.102669, 1024: 0.186009, 2048: 0.354364, 4096: 0.690570, 8192: 1.363543, 16384: 2.711788, 32768: 5.410873}
 
 
-def run_sweep():
+def run_sweep(emit):
     """The reference's two benchmark tables on one GPU, same shapes and timing style (warm-up, median of repeated
     CUDA-event timings, L2 flushed between repetitions): benchmarks/benchmark_lightning2.py:56-118 (b4 h32 d=e=128 bf16,
     fwd and bwd separately, with and without decay) and benchmarks/benchmark_srmsnorm.py (b12, dim 2048 bf16)."""
@@ -214,9 +214,9 @@ def run_sweep():
 
             bwd = timed(bwd_fn)
             units = B * H * n
-            print(json.dumps({"table": name, "n": n, "fwd_ms": fwd, "bwd_ms": bwd, "ref_fwd_ms": ref_f[n], "ref_bwd_ms": ref_b[n],
+            emit(json.dumps({"table": name, "n": n, "fwd_ms": fwd, "bwd_ms": bwd, "ref_fwd_ms": ref_f[n], "ref_bwd_ms": ref_b[n],
                               "tokens_per_s_fwd_bwd": B * n / ((fwd + bwd) * 1e-3),
-                              "hbm_frac_of_measured": ALG_BYTES_PER_UNIT * units / ((fwd + bwd) * 1e-3) / 1e9 / load_peaks()[0]}), flush=True)
+                              "hbm_frac_of_measured": ALG_BYTES_PER_UNIT * units / ((fwd + bwd) * 1e-3) / 1e9 / load_peaks()[0]}))
         del q, k, v, do
     for n in (512, 1024, 2048, 4096, 8192, 16384, 32768):
         x = torch.randn((12, n, 2048), device=dev, dtype=torch.bfloat16).requires_grad_()
@@ -231,12 +231,21 @@ def run_sweep():
 
         bwd = timed(bwd_fn)
         elems = 12 * n * 2048
-        print(json.dumps({"table": "srmsnorm", "n": n, "fwd_ms": fwd, "bwd_ms": bwd, "ref_fwd_ms": REF_SRMS_FWD[n], "ref_bwd_ms": REF_SRMS_BWD[n],
-                          "fwd_gbs": 4.0 * elems / fwd / 1e6, "bwd_gbs": 6.0 * elems / bwd / 1e6}), flush=True)
+        emit(json.dumps({"table": "srmsnorm", "n": n, "fwd_ms": fwd, "bwd_ms": bwd, "ref_fwd_ms": REF_SRMS_FWD[n], "ref_bwd_ms": REF_SRMS_BWD[n],
+                          "fwd_gbs": 4.0 * elems / fwd / 1e6, "bwd_gbs": 6.0 * elems / bwd / 1e6}))
 
 
 def main():
     global N_TOK
+    # Libraries (NCCL's version banner, for one) print to file descriptor 1; the contract is ONE JSON line on stdout.
+    # Everything that is not that line is sent to stderr by pointing fd 1 at fd 2 and keeping the real stdout aside.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        os.write(real_stdout, (line + "\n").encode())
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -258,10 +267,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, emit)
         return
     if args.sweep:
-        run_sweep()
+        run_sweep(emit)
         return
 
     import torch
@@ -478,7 +487,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "srmsnorm": srms, "long_context": sp,
         }
-        print(json.dumps(out), flush=True)
+        emit(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
 

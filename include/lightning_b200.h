@@ -92,6 +92,17 @@ int lab200_la_generic(const void* a, const void* bm, const void* c, const float*
                       int bh, int h, int n, int dk, int dv, int reverse, int state_only, int chunks,
                       int dtype, void* stream);
 
+/*
+ * Second half of a two-step use of lab200_la_generic, for callers that learn `state_in` only after the local states
+ * are known (sequence parallelism): step 1 is lab200_la_generic(..., state_only = 1) with a `state_out` buffer, which
+ * leaves the per-chunk states of the sequence (from a zero initial state) in `workspace`; step 2 is this call with the
+ * SAME bm, c, sizes, reverse, chunks and workspace: it adds the decayed `state_in` (may be NULL) to those states and runs
+ * only the block loop, so bm and c are not read a second time for states. No counterpart in the reference.
+ */
+int lab200_la_generic_resume(const void* a, const void* bm, const void* c, const float* slopes, void* out,
+                             const float* state_in, void* workspace, size_t workspace_bytes, int bh, int h,
+                             int n, int dk, int dv, int reverse, int chunks, int dtype, void* stream);
+
 /* o = LightningAttention2.forward(q, k, v, s): lightning_attn2.py:400-434 (with slopes) and
  * lightning_attn2_no_decay.py:368-400 (slopes = NULL). */
 int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slopes, void* o,

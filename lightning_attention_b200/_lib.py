@@ -39,6 +39,8 @@ def lib():
         L.lab200_la_workspace_bytes.argtypes = [i, i, i, i, i]
         L.lab200_la_generic.restype = i
         L.lab200_la_generic.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, i, i, vp]
+        L.lab200_la_generic_resume.restype = i
+        L.lab200_la_generic_resume.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, i, vp]
         L.lab200_la2_fwd.restype = i
         L.lab200_la2_fwd.argtypes = [vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, vp]
         L.lab200_la2_fwd_static.restype = i
@@ -59,7 +61,7 @@ def lib():
 
 EXPORTS = [
     "lab200_version", "lab200_launch_count", "lab200_la_debug_trace", "lab200_error_string", "lab200_la_plan_chunks", "lab200_la_workspace_bytes",
-    "lab200_la_generic", "lab200_la2_fwd", "lab200_la2_fwd_static", "lab200_la2_bwd", "lab200_la2_dkdv", "lab200_read_status",
+    "lab200_la_generic", "lab200_la_generic_resume", "lab200_la2_fwd", "lab200_la2_fwd_static", "lab200_la2_bwd", "lab200_la2_dkdv", "lab200_read_status",
     "lab200_srmsnorm_fwd", "lab200_srmsnorm_bwd",
 ]
 

@@ -213,7 +213,8 @@ int la_validate(const void* a, const void* bm, const void* c, const void* out, c
 // The generic product without the status reset (so that composite calls share one status word).
 int la_generic_impl(const void* a, const void* bm, const void* c, const float* slopes, void* out,
                     const float* state_in, float* state_out, void* workspace, size_t workspace_bytes, int bh, int h,
-                    int n, int dk, int dv, int reverse, int state_only, int chunks, int dtype, cudaStream_t st) {
+                    int n, int dk, int dv, int reverse, int state_only, int chunks, int dtype, cudaStream_t st,
+                    int resume = 0) {
   int rc = la_validate(a, bm, c, out, state_in, state_out, workspace, bh, h, n, dk, dv, state_only, dtype);
   if (rc != LAB200_OK) return rc;
   Tiling t;
@@ -261,6 +262,23 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
 
   // three phases: local chunk states -> decayed scan -> block loop per chunk with its incoming state
   float* states = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + WS_HEADER);
+  if (resume) {
+    // the workspace already holds the per-chunk prefix states of a preceding state-only call (zero initial state):
+    // add the decayed incoming state and go straight to the block loop
+    if (state_in != nullptr) {
+      const int elems_r = dv * dk;
+      const long long total_r = static_cast<long long>(bh) * elems_r;
+      la_rebase_kernel<<<static_cast<unsigned>((total_r + 255) / 256), 256, 0, st>>>(states, state_in, slopes, h, nchunks, elems_r,
+                                                                                  nblocks, bpc, p.reverse, total_r);
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
+    }
+    p.state_slots = nchunks;
+    p.chunk0 = 0;
+    p.state_in = states;
+    p.state_out = nullptr;
+    return launch_la(0, dtype, t, tA, tB, tC, tO, p, nchunks, bh, st);
+  }
   const bool need_total = (state_out != nullptr);
   const int skip_last = need_total ? 0 : 1;
   p.state_slots = nchunks;
@@ -517,6 +535,17 @@ int lab200_la_generic(const void* a, const void* bm, const void* c, const float*
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
   return la_generic_impl(a, bm, c, slopes, out, state_in, state_out, workspace, workspace_bytes, bh, h, n, dk, dv,
                          reverse, state_only, chunks, dtype, st);
+}
+
+int lab200_la_generic_resume(const void* a, const void* bm, const void* c, const float* slopes, void* out,
+                             const float* state_in, void* workspace, size_t workspace_bytes, int bh, int h, int n, int dk,
+                             int dv, int reverse, int chunks, int dtype, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = la_validate(a, bm, c, out, state_in, nullptr, workspace, bh, h, n, dk, dv, 0, dtype);
+  if (rc != LAB200_OK) return rc;
+  if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
+  return la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
+                         chunks, dtype, st, 1);
 }
 
 int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slopes, void* o, void* workspace,

@@ -499,4 +499,22 @@ __global__ void la_scan_kernel(float* __restrict__ states, const float* __restri
   if (total) total[idx] = run;
 }
 
+// Adds a state that arrives from outside the sequence to per-chunk prefix states that were computed from a zero
+// initial state: prefix[c] += lambda^(tokens between the sequence edge and chunk c) * init. Lets a caller compute the
+// local states first, learn the incoming state later (sequence parallelism) and still run the chunk pass only once.
+__global__ void la_rebase_kernel(float* __restrict__ states, const float* __restrict__ init,
+                                 const float* __restrict__ slopes, int h, int nchunks, int elems, int nblocks,
+                                 int blocks_per_chunk, int reverse, long long total_elems) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total_elems) return;
+  const int bh = static_cast<int>(idx / elems);
+  const int e = static_cast<int>(idx - static_cast<long long>(bh) * elems);
+  const float s = slopes ? slopes[bh % h] : 0.f;
+  const float v = init[idx];
+  for (int c = 0; c < nchunks; ++c) {
+    const int before = reverse ? (nblocks - min(nblocks, (c + 1) * blocks_per_chunk)) : c * blocks_per_chunk;
+    states[(static_cast<size_t>(bh) * nchunks + c) * elems + e] += __expf(-s * static_cast<float>(before * LA_BLOCK)) * v;
+  }
+}
+
 }  // namespace lab200

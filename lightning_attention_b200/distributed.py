@@ -80,12 +80,19 @@ def _shard_decay(s, h, shard_len, device):
 def combine_states(states, decay, rank, reverse=False):
     """State entering shard `rank` from the local states of all shards (list indexed by rank).
 
-    forward time: sum_{j<rank} decay^(rank-1-j) states[j];  reverse time: sum_{j>rank} decay^(j-rank-1) states[j]."""
-    order = range(len(states) - 1, rank, -1) if reverse else range(0, rank)
-    run = torch.zeros_like(states[0])
-    for j in order:
-        run = decay * run + states[j]
-    return run
+    forward time: sum_{j<rank} decay^(rank-1-j) states[j];  reverse time: sum_{j>rank} decay^(j-rank-1) states[j].
+    One stacked weighted sum (a handful of kernel launches whatever the number of ranks)."""
+    R = len(states)
+    idx = torch.arange(R, device=states[0].device)
+    expo = (idx - rank - 1) if reverse else (rank - 1 - idx)  # >= 0 exactly for the shards that contribute
+    use = expo >= 0
+    if not bool(use.any()):
+        return torch.zeros_like(states[0])
+    h = decay.numel()
+    w = decay.reshape(1, h).to(torch.float32) ** expo.clamp(min=0).reshape(R, 1).to(torch.float32)  # 0 ** 0 == 1
+    w = torch.where(use.reshape(R, 1), w, torch.zeros_like(w))
+    stacked = torch.stack([t.to(torch.float32) for t in states], dim=0)  # (R, b, h, x, y)
+    return torch.einsum("rh,rbhxy->bhxy", w, stacked).to(states[0].dtype)
 
 
 def exchange_states(local_state, group=None):
@@ -110,10 +117,11 @@ class _SequenceParallelAttention(torch.autograd.Function):
             raise RuntimeError(f"sequence-parallel shards must be multiples of {BLOCK} tokens, got {L}")
         rank = dist.get_rank(group)
         decay = _shard_decay(s, h, L, q.device)
-        # state this shard contributes, (b, h, e, d) = KV^T, from a zero initial state
-        _, s_loc = product(None, k, v, s, reverse=False, state_only=True)
+        # state this shard contributes, (b, h, e, d) = KV^T, from a zero initial state; the per-chunk states computed
+        # on the way are kept and reused by the second call, which then only runs the block loop
+        _, s_loc, handle = product(None, k, v, s, reverse=False, state_only=True, keep_workspace=True)
         kv_in = combine_states(exchange_states(s_loc, group), decay, rank, reverse=False)
-        o, _ = product(q, k, v, s, reverse=False, state_in=kv_in)
+        o, _ = product(q, k, v, s, reverse=False, state_in=kv_in, resume_from=handle)
         ctx.save_for_backward(q, k, v, s if s is not None else torch.empty(0), kv_in)
         ctx.has_s = s is not None
         ctx.group, ctx.product = group, product
@@ -131,9 +139,9 @@ class _SequenceParallelAttention(torch.autograd.Function):
         # dq_t = sum_{j<=t} lambda^(t-j) (do_t . v_j) k_j : forward time, incoming state = KV_in (d x e layout)
         dq, _ = product(do, v, k, s, reverse=False, state_in=kv_in.transpose(2, 3).contiguous())
         # reverse-time state of this shard for dk: (b, h, d, e) = sum_t lambda^t q_t^T do_t
-        _, ds_loc = product(None, do, q, s, reverse=True, state_only=True)
+        _, ds_loc, handle = product(None, do, q, s, reverse=True, state_only=True, keep_workspace=True)
         dkv_in = combine_states(exchange_states(ds_loc, group), decay, rank, reverse=True)
-        dk, _ = product(v, do, q, s, reverse=True, state_in=dkv_in)
+        dk, _ = product(v, do, q, s, reverse=True, state_in=dkv_in, resume_from=handle)
         dv, _ = product(k, q, do, s, reverse=True, state_in=dkv_in.transpose(2, 3).contiguous())
         return dq, dk, dv, None, None, None
 

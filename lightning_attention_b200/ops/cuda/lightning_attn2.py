@@ -26,12 +26,17 @@ def _workspace(nbytes, device):
     return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
 
 
-def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0):
+def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0,
+               keep_workspace=False, resume_from=None):
     """The decayed causal product all attention results are instances of (see include/lightning_b200.h).
 
     a, bm: (b, h, n, dk); c: (b, h, n, dv). Returns (out, state_out) with out (b, h, n, dv) in the
     input dtype (None when state_only) and state_out (b, h, dv, dk) fp32 (None unless requested).
     state_in, if given, has the shape of state_out and is the running state entering the sequence.
+
+    Two-step use (sequence parallelism): call with state_only=True, keep_workspace=True -> (None, state, handle);
+    later call with the same bm, c, s, reverse, chunks and resume_from=handle (plus the now known state_in):
+    the per-chunk states computed in step one are reused instead of being computed again.
     """
     _lib.require_cuda(a, bm, c)
     b, h, n, dk = bm.shape
@@ -46,8 +51,18 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
         state_in = state_in.to(device=dev, dtype=torch.float32).contiguous()
         if tuple(state_in.shape) != (b, h, dv, dk):
             raise RuntimeError(f"state_in must have shape {(b, h, dv, dk)}, got {tuple(state_in.shape)}")
-    state_out = torch.empty((b, h, dv, dk), dtype=torch.float32, device=dev) if (want_state or state_only) else None
     L = _lib.lib()
+    if resume_from is not None:
+        ws, nbytes, key = resume_from
+        if key != (b, h, n, dk, dv, bool(reverse), int(chunks), bm.dtype):
+            raise RuntimeError("resume_from does not belong to a state-only call with the same sizes and options")
+        with torch.cuda.device(dev):
+            rc = L.lab200_la_generic_resume(
+                _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in), ws.data_ptr(),
+                nbytes, b * h, h, n, dk, dv, int(bool(reverse)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
+        _lib.check(rc, "lab200_la_generic_resume")
+        return out, None
+    state_out = torch.empty((b, h, dv, dk), dtype=torch.float32, device=dev) if (want_state or state_only) else None
     nbytes = L.lab200_la_workspace_bytes(b * h, n, dk, dv, chunks)
     ws = _workspace(nbytes, dev)
     with torch.cuda.device(dev):
@@ -56,6 +71,8 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
             _lib.ptr(state_out), ws.data_ptr(), nbytes, b * h, h, n, dk, dv, int(bool(reverse)),
             int(bool(state_only)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
     _lib.check(rc, "lab200_la_generic")
+    if keep_workspace:
+        return out, state_out, (ws, nbytes, (b, h, n, dk, dv, bool(reverse), int(chunks), bm.dtype))
     return out, state_out
 
 

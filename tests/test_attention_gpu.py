@@ -314,3 +314,21 @@ def test_fused_dk_dv_sweep(cuda_lib, b, h, n, d, e, decay):
     _, _, gdk, gdv = run_fwd_bwd(fn, q, k, v, do)
     assert_parity(dk, gdk.float(), "fused-vs-generic:dk", False)
     assert_parity(dv, gdv.float(), "fused-vs-generic:dv", False)
+
+
+@pytest.mark.parametrize("reverse", [False, True])
+@pytest.mark.parametrize("chunks", [1, 3])
+def test_two_step_generic_call_reuses_chunk_states(cuda_lib, reverse, chunks):
+    """state-only call + lab200_la_generic_resume with an incoming state == one call with that state."""
+    torch.manual_seed(9)
+    b, h, n, dk, dv = 1, 3, 1536, 128, 64
+    a, bm = (torch.randn((b, h, n, dk), device=DEV).bfloat16() for _ in range(2))
+    c = torch.randn((b, h, n, dv), device=DEV).bfloat16()
+    s = (la._build_slope_tensor(h).reshape(-1) * 0.02).to(DEV)
+    st_in = torch.randn((b, h, dv, dk), device=DEV)
+    ref, _ = la_generic(a, bm, c, s, reverse=reverse, state_in=st_in, chunks=chunks)
+    _, st_loc, handle = la_generic(None, bm, c, s, reverse=reverse, state_only=True, chunks=chunks, keep_workspace=True)
+    got, _ = la_generic(a, bm, c, s, reverse=reverse, state_in=st_in, chunks=chunks, resume_from=handle)
+    assert_parity(got, ref.float(), "two-step", False)
+    _, st_loc2 = la_generic(None, bm, c, s, reverse=reverse, state_only=True, chunks=chunks)
+    assert torch.equal(st_loc, st_loc2)

@@ -20,15 +20,22 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def oracle_product(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0):
-    """Same call signature as the CUDA op `la_generic`, computed by the numpy oracle in fp64."""
+def oracle_product(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0,
+                   keep_workspace=False, resume_from=None):
+    """Same call signature as the CUDA op `la_generic`, computed by the numpy oracle in fp64. The two-step protocol
+    (keep_workspace / resume_from) is honoured by handing back a token and checking that it comes back."""
     from oracle import lightning_oracle as O
 
     f = lambda t: None if t is None else t.detach().double().numpy()
     a_ = f(a) if a is not None else np.zeros_like(f(bm))
     out, st = O.la_generic(a_, f(bm), f(c), f(s), reverse=reverse, state_in=f(state_in))
     out_t = None if state_only else torch.from_numpy(np.ascontiguousarray(out))
-    return out_t, torch.from_numpy(np.ascontiguousarray(st)).float().double()
+    st_t = torch.from_numpy(np.ascontiguousarray(st)).float().double()
+    if resume_from is not None:
+        assert resume_from == ("handle", tuple(bm.shape), tuple(c.shape), bool(reverse))
+    if keep_workspace:
+        return out_t, st_t, ("handle", tuple(bm.shape), tuple(c.shape), bool(reverse))
+    return out_t, st_t
 
 
 def _sp_worker(rank, world, port, scale, result_dir):
