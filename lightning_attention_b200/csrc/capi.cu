@@ -68,7 +68,7 @@ int make_tmap(CUtensorMap* tm, const void* ptr, int bh, int n, int dim, int dtyp
 }
 
 struct Tiling {
-  int nks, nvs, nslices, nstage_full;
+  int nks, nvs, nslices;
 };
 
 bool pick_tiling(int dk, int dv, Tiling* t) {
