@@ -152,6 +152,8 @@ ORACLE_CASES = [
     (1, 2, 256, 256, 256, True, 2, True),
     (1, 1, 1, 16, 16, False, 1, False),
     (1, 1, 129, 32, 32, True, 2, False),
+    (1, 2, 384, 128, 256, False, 1, True),   # two dv slices per (batch, head) in the pipelined kernel
+    (1, 2, 256, 64, 192, True, 2, True),     # dv = 128 + 64: a full and a half-empty slice
 ]
 
 
