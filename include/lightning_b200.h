@@ -103,6 +103,34 @@ int lab200_la_generic_resume(const void* a, const void* bm, const void* c, const
                              const float* state_in, void* workspace, size_t workspace_bytes, int bh, int h,
                              int n, int dk, int dv, int reverse, int chunks, int dtype, void* stream);
 
+/*
+ * lab200_la_generic_resume for the product with Bm and C exchanged (dk == dv only). The states a product keeps per
+ * chunk are sum lambda^.. bm_t^T c_t laid out (dv, dk); exchanging bm and c transposes them, which is how dk and dv
+ * (and forward and dq) are related. `workspace` must come from a call - state-only, full or resumed - on (c, bm) with the
+ * same sizes, reverse and chunks; its states are transposed in place (the workspace then belongs to THIS product) and only
+ * the block loop runs. rebase != 0: those states started from a zero initial state and the decayed `state_in` is added;
+ * rebase == 0: they already include the incoming state. `state_in` ((bh, dv, dk), this product's layout) must be given
+ * either way when there is an incoming state: a sequence that is not cut into chunks uses it directly.
+ * No counterpart in the reference.
+ */
+int lab200_la_generic_resume_swapped(const void* a, const void* bm, const void* c, const float* slopes, void* out,
+                                     const float* state_in, void* workspace, size_t workspace_bytes, int bh,
+                                     int h, int n, int dk, int dv, int reverse, int chunks, int rebase, int dtype,
+                                     void* stream);
+
+/*
+ * Sequence parallelism: the state entering this rank's shard from the all-gathered shard states.
+ * gathered: (ranks, bh, x, y) fp32, entry r = the state shard r contributes from a zero initial state
+ * (lab200_la_generic state_out, x = dv, y = dk); every shard holds `shard_tokens` tokens.
+ *   reverse == 0:  out = sum_{r < rank} lambda^((rank-1-r) shard_tokens) gathered[r]
+ *   reverse != 0:  out = sum_{r > rank} lambda^((r-rank-1) shard_tokens) gathered[r]
+ * out: (bh, x, y) and/or out_t: (bh, y, x), the same state transposed (for the product with Bm and C exchanged);
+ * either may be NULL. One launch, no workspace. No counterpart in the reference (it is single-GPU).
+ */
+int lab200_la_combine_states(const float* gathered, const float* slopes, float* out, float* out_t, int ranks,
+                             int rank, int bh, int h, int x, int y, long long shard_tokens, int reverse,
+                             void* stream);
+
 /* o = LightningAttention2.forward(q, k, v, s): lightning_attn2.py:400-434 (with slopes) and
  * lightning_attn2_no_decay.py:368-400 (slopes = NULL). */
 int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slopes, void* o,

@@ -211,6 +211,17 @@ int la_validate(const void* a, const void* bm, const void* c, const void* out, c
                 int dtype);
 
 // The generic product without the status reset (so that composite calls share one status word).
+enum : int { RESUME = 1, RESUME_SWAPPED = 2, RESUME_NO_REBASE = 4 };
+
+// Number of chunks la_generic_impl cuts the sequence into.
+int chunk_count(int bh, int n, int dk, int dv, int chunks) {
+  const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
+  int nchunks = chunks > 0 ? chunks : plan_chunks(bh, n, dk, dv);
+  if (nchunks > nblocks) nchunks = nblocks;
+  const int bpc = (nblocks + nchunks - 1) / nchunks;
+  return (nblocks + bpc - 1) / bpc;  // drop empty trailing chunks
+}
+
 int la_generic_impl(const void* a, const void* bm, const void* c, const float* slopes, void* out,
                     const float* state_in, float* state_out, void* workspace, size_t workspace_bytes, int bh, int h,
                     int n, int dk, int dv, int reverse, int state_only, int chunks, int dtype, cudaStream_t st,
@@ -220,10 +231,8 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   Tiling t;
   pick_tiling(dk, dv, &t);
   const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
-  int nchunks = chunks > 0 ? chunks : plan_chunks(bh, n, dk, dv);
-  if (nchunks > nblocks) nchunks = nblocks;
+  const int nchunks = chunk_count(bh, n, dk, dv, chunks);
   const int bpc = (nblocks + nchunks - 1) / nchunks;
-  nchunks = (nblocks + bpc - 1) / bpc;  // drop empty trailing chunks
   if (nchunks > 65535) return LAB200_ERR_SHAPE;
   const size_t need = WS_HEADER + (nchunks > 1 ? static_cast<size_t>(bh) * nchunks * dv * dk * sizeof(float) : 0);
   if (!workspace || workspace_bytes < need) return LAB200_ERR_WORKSPACE;
@@ -263,9 +272,17 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   // three phases: local chunk states -> decayed scan -> block loop per chunk with its incoming state
   float* states = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + WS_HEADER);
   if (resume) {
-    // the workspace already holds the per-chunk prefix states of a preceding state-only call (zero initial state):
-    // add the decayed incoming state and go straight to the block loop
-    if (state_in != nullptr) {
+    // the workspace already holds the per-chunk prefix states of a preceding call: go straight to the block loop.
+    // RESUME_SWAPPED: they belong to the product with Bm and C exchanged, i.e. they are the transposes (dk == dv).
+    // Unless RESUME_NO_REBASE is set they were computed from a zero initial state and the decayed incoming state is added.
+    if (resume & RESUME_SWAPPED) {
+      if (dk != dv) return LAB200_ERR_SHAPE;
+      const int nt = (dk + 31) / 32;
+      la_transpose_square_kernel<<<dim3(static_cast<unsigned>(bh) * nchunks, nt * (nt + 1) / 2), dim3(32, 8), 0, st>>>(states, dk);
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
+    }
+    if (state_in != nullptr && !(resume & RESUME_NO_REBASE)) {
       const int elems_r = dv * dk;
       const long long total_r = static_cast<long long>(bh) * elems_r;
       la_rebase_kernel<<<static_cast<unsigned>((total_r + 255) / 256), 256, 0, st>>>(states, state_in, slopes, h, nchunks, elems_r,
@@ -545,7 +562,32 @@ int lab200_la_generic_resume(const void* a, const void* bm, const void* c, const
   if (rc != LAB200_OK) return rc;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
   return la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
-                         chunks, dtype, st, 1);
+                         chunks, dtype, st, RESUME);
+}
+
+int lab200_la_generic_resume_swapped(const void* a, const void* bm, const void* c, const float* slopes, void* out,
+                                     const float* state_in, void* workspace, size_t workspace_bytes, int bh, int h, int n,
+                                     int dk, int dv, int reverse, int chunks, int rebase, int dtype, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dk != dv) return LAB200_ERR_SHAPE;
+  int rc = la_validate(a, bm, c, out, state_in, nullptr, workspace, bh, h, n, dk, dv, 0, dtype);
+  if (rc != LAB200_OK) return rc;
+  if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
+  return la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
+                         chunks, dtype, st, RESUME | RESUME_SWAPPED | (rebase ? 0 : RESUME_NO_REBASE));
+}
+
+int lab200_la_combine_states(const float* gathered, const float* slopes, float* out, float* out_t, int ranks, int rank,
+                             int bh, int h, int x, int y, long long shard_tokens, int reverse, void* stream) {
+  if (!gathered || (!out && !out_t) || ranks < 1 || rank < 0 || rank >= ranks || bh < 1 || h < 1 || x < 1 || y < 1 ||
+      shard_tokens < 0 || bh > 65535)
+    return LAB200_ERR_SHAPE;
+  if (!aligned16(gathered) || !aligned16(out) || !aligned16(out_t)) return LAB200_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  la_combine_kernel<<<dim3((y + 31) / 32, (x + 31) / 32, bh), dim3(32, 8), 0, st>>>(
+      gathered, slopes, out, out_t, ranks, rank, bh, h, x, y, static_cast<float>(shard_tokens), reverse ? 1 : 0);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
 }
 
 int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slopes, void* o, void* workspace,
@@ -607,8 +649,11 @@ int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slo
   rc = la_generic_impl(v, dout, q, slopes, dk, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, e, d, 1, 0,
                        chunks, dtype, st);
   if (rc != LAB200_OK) return rc;
+  // In chunk mode the dk launch leaves the reverse-time state entering every chunk, sum lambda^t q_t^T do_t as (d, e), in
+  // the workspace; dv needs the same states as (e, d). With d == e they are transposed in place instead of recomputed.
+  const int resume = (d == e && chunk_count(bh, n, e, d, chunks) > 1) ? (RESUME | RESUME_SWAPPED | RESUME_NO_REBASE) : 0;
   return la_generic_impl(k, q, dout, slopes, dv, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, d, e, 1, 0,
-                         chunks, dtype, st);
+                         chunks, dtype, st, resume);
 }
 
 int lab200_la2_dkdv(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dk,

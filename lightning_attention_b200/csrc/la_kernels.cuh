@@ -517,4 +517,76 @@ __global__ void la_rebase_kernel(float* __restrict__ states, const float* __rest
   }
 }
 
+// State entering this rank's sequence shard from the all-gathered local shard states (sequence parallelism):
+//   forward time:  out = sum_{r < rank} lambda^((rank-1-r) L) gathered[r]
+//   reverse time:  out = sum_{r > rank} lambda^((r-rank-1) L) gathered[r]
+// gathered is (R, bh, X, Y) fp32, L the tokens per shard. `out` (bh, X, Y) and/or `out_t` (bh, Y, X, the same state
+// for the product with Bm and C exchanged) may be null. Grid (ceil(Y/32), ceil(X/32), bh), block (32, 8).
+__global__ void la_combine_kernel(const float* __restrict__ gathered, const float* __restrict__ slopes,
+                                  float* __restrict__ out, float* __restrict__ out_t, int R, int rank, int bh_total, int h,
+                                  int X, int Y, float shard_tokens, int reverse) {
+  __shared__ float tile[32][33];
+  const int bh = blockIdx.z;
+  const int x0 = blockIdx.y * 32, y0 = blockIdx.x * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const float s = slopes ? slopes[bh % h] : 0.f;
+  const int r_begin = reverse ? rank + 1 : 0, r_end = reverse ? R : rank;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int y = y0 + tx;
+  for (int r = r_begin; r < r_end; ++r) {
+    const int expo = reverse ? (r - rank - 1) : (rank - 1 - r);
+    const float w = expf(-s * shard_tokens * static_cast<float>(expo));
+    const float* src = gathered + (static_cast<size_t>(r) * bh_total + bh) * X * Y;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int x = x0 + ty + 8 * k;
+      if (x < X && y < Y) acc[k] = fmaf(w, src[static_cast<size_t>(x) * Y + y], acc[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int x = x0 + ty + 8 * k;
+    if (out && x < X && y < Y) out[(static_cast<size_t>(bh) * X + x) * Y + y] = acc[k];
+    tile[ty + 8 * k][tx] = acc[k];
+  }
+  if (out_t) {
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int yy = y0 + ty + 8 * k, xx = x0 + tx;  // out_t[yy][xx] = state[xx][yy]
+      if (yy < Y && xx < X) out_t[(static_cast<size_t>(bh) * Y + yy) * X + xx] = tile[tx][ty + 8 * k];
+    }
+  }
+}
+
+// In-place transpose of `count` square D x D fp32 matrices stored back to back (the per-chunk states of a product,
+// turned into those of the product with Bm and C exchanged). Grid (count, tile pairs i <= j), block (32, 8).
+__global__ void la_transpose_square_kernel(float* __restrict__ m, int D) {
+  __shared__ float ta[32][33], tb[32][33];
+  const int nt = (D + 31) / 32;
+  int pair = blockIdx.y, ti = 0;
+  for (; ti < nt && pair >= nt - ti; ++ti) pair -= nt - ti;  // row ti of the upper triangle of tile pairs
+  if (ti >= nt) return;
+  const int tj = ti + pair;
+  float* base = m + static_cast<size_t>(blockIdx.x) * D * D;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = ty + 8 * k;
+    const int ai = ti * 32 + r, aj = tj * 32 + tx;  // tile (ti, tj)
+    const int bi = tj * 32 + r, bj = ti * 32 + tx;  // tile (tj, ti)
+    ta[r][tx] = (ai < D && aj < D) ? base[static_cast<size_t>(ai) * D + aj] : 0.f;
+    tb[r][tx] = (bi < D && bj < D) ? base[static_cast<size_t>(bi) * D + bj] : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = ty + 8 * k;
+    const int ai = ti * 32 + r, aj = tj * 32 + tx;
+    const int bi = tj * 32 + r, bj = ti * 32 + tx;
+    if (ai < D && aj < D) base[static_cast<size_t>(ai) * D + aj] = tb[tx][r];
+    if (ti != tj && bi < D && bj < D) base[static_cast<size_t>(bi) * D + bj] = ta[tx][r];
+  }
+}
+
 }  // namespace lab200

@@ -14,7 +14,10 @@ The reference is single-GPU only; both modes below are derived from its recurren
        KV_in[0] = 0,   KV_in[r] = sum_{j<r} lambda^((r-1-j) L) S_j,
 
    and runs the single-GPU forward with KV_in[r] as its initial state. The backward pass does the same in
-   reverse time for dKV (ranks after r), and reuses KV_in for dq.
+   reverse time for dKV (ranks after r), and reuses KV_in for dq. Per forward+backward that is two all-gathers and two
+   one-launch combines; nothing in between waits on the host. The chunk states a product computes on the way are kept
+   and reused: by its own block loop once the incoming state is known, and (d == e) by the product with k and v
+   exchanged, whose states are the transposes (forward -> dq, dk -> dv).
 
 The device arithmetic is injected as `product` (default: the CUDA op `la_generic`), which keeps the
 exchange logic testable on CPU ranks (gloo) with any other implementation of the same product.
@@ -78,21 +81,23 @@ def _shard_decay(s, h, shard_len, device):
 
 
 def combine_states(states, decay, rank, reverse=False):
-    """State entering shard `rank` from the local states of all shards (list indexed by rank).
+    """State entering shard `rank` from the local states of all shards (list indexed by rank, or one stacked tensor).
 
     forward time: sum_{j<rank} decay^(rank-1-j) states[j];  reverse time: sum_{j>rank} decay^(j-rank-1) states[j].
-    One stacked weighted sum (a handful of kernel launches whatever the number of ranks)."""
-    R = len(states)
-    idx = torch.arange(R, device=states[0].device)
-    expo = (idx - rank - 1) if reverse else (rank - 1 - idx)  # >= 0 exactly for the shards that contribute
-    use = expo >= 0
-    if not bool(use.any()):
-        return torch.zeros_like(states[0])
+    Plain torch, any device, no host synchronisation; the CUDA path of `lightning_attn_sp` uses the one-launch kernel
+    behind `combine_gathered` instead."""
+    stacked = states if torch.is_tensor(states) else torch.stack(list(states), dim=0)  # (R, b, h, x, y)
+    R = stacked.shape[0]
+    expo = [(j - rank - 1) if reverse else (rank - 1 - j) for j in range(R)]  # >= 0 exactly for the shards that contribute
+    if not any(x >= 0 for x in expo):
+        return torch.zeros_like(stacked[0])
     h = decay.numel()
-    w = decay.reshape(1, h).to(torch.float32) ** expo.clamp(min=0).reshape(R, 1).to(torch.float32)  # 0 ** 0 == 1
-    w = torch.where(use.reshape(R, 1), w, torch.zeros_like(w))
-    stacked = torch.stack([t.to(torch.float32) for t in states], dim=0)  # (R, b, h, x, y)
-    return torch.einsum("rh,rbhxy->bhxy", w, stacked).to(states[0].dtype)
+    dev = stacked.device
+    pw = torch.tensor([max(x, 0) for x in expo], dtype=torch.float32, device=dev).reshape(R, 1)
+    use = torch.tensor([x >= 0 for x in expo], device=dev).reshape(R, 1)
+    w = decay.reshape(1, h).to(torch.float32) ** pw  # 0 ** 0 == 1
+    w = torch.where(use, w, torch.zeros_like(w))
+    return torch.einsum("rh,rbhxy->bhxy", w, stacked.to(torch.float32)).to(stacked.dtype)
 
 
 def exchange_states(local_state, group=None):
@@ -101,6 +106,39 @@ def exchange_states(local_state, group=None):
     out = [torch.empty_like(local_state) for _ in range(world)]
     dist.all_gather(out, local_state.contiguous(), group=group)
     return out
+
+
+def gather_states(local_state, group=None):
+    """All-gather of the per-rank local states into ONE tensor (world, b, h, x, y): a single collective, no copies."""
+    world = dist.get_world_size(group)
+    local_state = local_state.contiguous()
+    flat = torch.empty((world * local_state.shape[0],) + tuple(local_state.shape[1:]), dtype=local_state.dtype,
+                       device=local_state.device)
+    dist.all_gather_into_tensor(flat, local_state, group=group)
+    return flat.view((world,) + tuple(local_state.shape))
+
+
+def combine_gathered(gathered, s, shard_len, rank, reverse=False):
+    """(state_in, state_in transposed) for shard `rank` from `gather_states` output (world, b, h, x, y).
+
+    CUDA tensors: one launch of the library's combine kernel (lab200_la_combine_states) writes both layouts.
+    Other devices (the gloo tests of the exchange logic): the torch formula of `combine_states`."""
+    R, b, h, x, y = gathered.shape
+    if gathered.is_cuda:
+        from . import _lib
+
+        dev = gathered.device
+        g = gathered.to(torch.float32).contiguous()
+        sl = None if s is None else s.detach().to(device=dev, dtype=torch.float32).reshape(-1)[:h].contiguous()
+        out = torch.empty((b, h, x, y), dtype=torch.float32, device=dev)
+        out_t = torch.empty((b, h, y, x), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().lab200_la_combine_states(g.data_ptr(), _lib.ptr(sl), out.data_ptr(), out_t.data_ptr(), R, rank,
+                                                     b * h, h, x, y, int(shard_len), int(bool(reverse)), _lib.stream_ptr(dev))
+        _lib.check(rc, "lab200_la_combine_states")
+        return out, out_t
+    out = combine_states(gathered, _shard_decay(s, h, shard_len, gathered.device), rank, reverse=reverse)
+    return out, out.transpose(2, 3).contiguous()
 
 
 def _default_product():
@@ -116,33 +154,41 @@ class _SequenceParallelAttention(torch.autograd.Function):
         if L % BLOCK != 0:
             raise RuntimeError(f"sequence-parallel shards must be multiples of {BLOCK} tokens, got {L}")
         rank = dist.get_rank(group)
-        decay = _shard_decay(s, h, L, q.device)
         # state this shard contributes, (b, h, e, d) = KV^T, from a zero initial state; the per-chunk states computed
         # on the way are kept and reused by the second call, which then only runs the block loop
         _, s_loc, handle = product(None, k, v, s, reverse=False, state_only=True, keep_workspace=True)
-        kv_in = combine_states(exchange_states(s_loc, group), decay, rank, reverse=False)
-        o, _ = product(q, k, v, s, reverse=False, state_in=kv_in, resume_from=handle)
-        ctx.save_for_backward(q, k, v, s if s is not None else torch.empty(0), kv_in)
+        kv_in, kv_in_t = combine_gathered(gather_states(s_loc, group), s, L, rank, reverse=False)
+        o, _, handle = product(q, k, v, s, reverse=False, state_in=kv_in, resume_from=handle, keep_workspace=True)
+        ctx.save_for_backward(q, k, v, s if s is not None else torch.empty(0), kv_in_t)
         ctx.has_s = s is not None
         ctx.group, ctx.product = group, product
+        ctx.kv_handle = handle if d == v.shape[-1] else None  # chunk states of (k, v), incoming state included
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, s, kv_in = ctx.saved_tensors
+        q, k, v, s, kv_in_t = ctx.saved_tensors
         s = s if ctx.has_s else None
         group, product = ctx.group, ctx.product
         b, h, L, d = q.shape
         rank = dist.get_rank(group)
-        decay = _shard_decay(s, h, L, q.device)
         do = do.contiguous()
-        # dq_t = sum_{j<=t} lambda^(t-j) (do_t . v_j) k_j : forward time, incoming state = KV_in (d x e layout)
-        dq, _ = product(do, v, k, s, reverse=False, state_in=kv_in.transpose(2, 3).contiguous())
+        # dq_t = sum_{j<=t} lambda^(t-j) (do_t . v_j) k_j : forward time, incoming state = KV_in in (d, e) layout. Its chunk
+        # states are the transposes of the forward's, which are still in the kept workspace (used once: a second backward
+        # through the same graph recomputes them).
+        handle, ctx.kv_handle = ctx.kv_handle, None
+        if handle is not None:
+            dq, _ = product(do, v, k, s, reverse=False, state_in=kv_in_t, resume_from=handle, resume_swapped=True, rebase=False)
+        else:
+            dq, _ = product(do, v, k, s, reverse=False, state_in=kv_in_t)
         # reverse-time state of this shard for dk: (b, h, d, e) = sum_t lambda^t q_t^T do_t
         _, ds_loc, handle = product(None, do, q, s, reverse=True, state_only=True, keep_workspace=True)
-        dkv_in = combine_states(exchange_states(ds_loc, group), decay, rank, reverse=True)
-        dk, _ = product(v, do, q, s, reverse=True, state_in=dkv_in, resume_from=handle)
-        dv, _ = product(k, q, do, s, reverse=True, state_in=dkv_in.transpose(2, 3).contiguous())
+        dkv_in, dkv_in_t = combine_gathered(gather_states(ds_loc, group), s, L, rank, reverse=True)
+        dk, _, handle = product(v, do, q, s, reverse=True, state_in=dkv_in, resume_from=handle, keep_workspace=True)
+        if d == v.shape[-1]:
+            dv, _ = product(k, q, do, s, reverse=True, state_in=dkv_in_t, resume_from=handle, resume_swapped=True, rebase=False)
+        else:
+            dv, _ = product(k, q, do, s, reverse=True, state_in=dkv_in_t)
         return dq, dk, dv, None, None, None
 
 

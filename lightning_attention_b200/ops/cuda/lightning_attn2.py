@@ -26,8 +26,22 @@ def _workspace(nbytes, device):
     return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
 
 
+class KeptWorkspace:
+    """Workspace of a chunked product kept for a later resume: the buffer, the product it belongs to (sizes, options and
+    the addresses of bm and c) and whether the state entering the sequence is already part of its chunk states."""
+    __slots__ = ("ws", "nbytes", "key", "based")
+
+    def __init__(self, ws, nbytes, key, based):
+        self.ws, self.nbytes, self.key, self.based = ws, nbytes, key, based
+
+
+def _product_key(bm, c, reverse, chunks):
+    b, h, n, dk = bm.shape
+    return (b, h, n, dk, c.shape[-1], bool(reverse), int(chunks), bm.dtype, bm.data_ptr(), c.data_ptr())
+
+
 def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0,
-               keep_workspace=False, resume_from=None):
+               keep_workspace=False, resume_from=None, resume_swapped=False, rebase=True):
     """The decayed causal product all attention results are instances of (see include/lightning_b200.h).
 
     a, bm: (b, h, n, dk); c: (b, h, n, dv). Returns (out, state_out) with out (b, h, n, dv) in the
@@ -37,11 +51,18 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
     Two-step use (sequence parallelism): call with state_only=True, keep_workspace=True -> (None, state, handle);
     later call with the same bm, c, s, reverse, chunks and resume_from=handle (plus the now known state_in):
     the per-chunk states computed in step one are reused instead of being computed again.
+    resume_swapped=True (dk == dv): the handle comes from the product with bm and c exchanged, whose chunk states are the
+    transposes of this one's (dk and dv, forward and dq are such pairs); they are transposed in place and the handle then
+    belongs to this product. rebase=False says the kept states already include the incoming state (the handle went through
+    a resumed call); state_in must still be passed, in this product's layout, for sequences that are not cut into chunks.
+    Any call with keep_workspace=True returns (out, state_out, handle).
     """
     _lib.require_cuda(a, bm, c)
     b, h, n, dk = bm.shape
     dv = c.shape[-1]
     dev = bm.device
+    if (resume_from is not None or keep_workspace) and not (bm.is_contiguous() and c.is_contiguous()):
+        raise RuntimeError("keep_workspace / resume_from need contiguous bm and c (the handle is tied to their storage)")
     bm = bm.contiguous()
     c = c.contiguous()
     a = None if state_only else a.contiguous()
@@ -52,15 +73,33 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
         if tuple(state_in.shape) != (b, h, dv, dk):
             raise RuntimeError(f"state_in must have shape {(b, h, dv, dk)}, got {tuple(state_in.shape)}")
     L = _lib.lib()
+    if resume_from is None and (resume_swapped or not rebase):
+        raise RuntimeError("resume_swapped / rebase=False need resume_from")
+    if resume_from is not None and not resume_swapped and not rebase:
+        raise RuntimeError("rebase=False is only available together with resume_swapped")
     if resume_from is not None:
-        ws, nbytes, key = resume_from
-        if key != (b, h, n, dk, dv, bool(reverse), int(chunks), bm.dtype):
-            raise RuntimeError("resume_from does not belong to a state-only call with the same sizes and options")
+        hd = resume_from
+        want_key = _product_key(c, bm, reverse, chunks) if resume_swapped else _product_key(bm, c, reverse, chunks)
+        if not isinstance(hd, KeptWorkspace) or hd.key != want_key:
+            raise RuntimeError("resume_from does not belong to a call on the same tensors with the same sizes and options")
+        if state_in is not None and hd.based == bool(rebase):
+            raise RuntimeError("the kept chunk states already include the incoming state" if hd.based else
+                               "the kept chunk states do not include the incoming state yet")
         with torch.cuda.device(dev):
-            rc = L.lab200_la_generic_resume(
-                _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in), ws.data_ptr(),
-                nbytes, b * h, h, n, dk, dv, int(bool(reverse)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
+            if resume_swapped:
+                rc = L.lab200_la_generic_resume_swapped(
+                    _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in), hd.ws.data_ptr(),
+                    hd.nbytes, b * h, h, n, dk, dv, int(bool(reverse)), int(chunks), int(bool(rebase)),
+                    _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
+            else:
+                rc = L.lab200_la_generic_resume(
+                    _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in), hd.ws.data_ptr(),
+                    hd.nbytes, b * h, h, n, dk, dv, int(bool(reverse)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
         _lib.check(rc, "lab200_la_generic_resume")
+        hd.key = _product_key(bm, c, reverse, chunks)  # a swapped resume hands the workspace over to this product
+        hd.based = True
+        if keep_workspace:
+            return out, None, hd
         return out, None
     state_out = torch.empty((b, h, dv, dk), dtype=torch.float32, device=dev) if (want_state or state_only) else None
     nbytes = L.lab200_la_workspace_bytes(b * h, n, dk, dv, chunks)
@@ -72,7 +111,7 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
             int(bool(state_only)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
     _lib.check(rc, "lab200_la_generic")
     if keep_workspace:
-        return out, state_out, (ws, nbytes, (b, h, n, dk, dv, bool(reverse), int(chunks), bm.dtype))
+        return out, state_out, KeptWorkspace(ws, nbytes, _product_key(bm, c, reverse, chunks), based=not state_only)
     return out, state_out
 
 
@@ -108,6 +147,29 @@ def _bwd(q, k, v, sl, do, chunks=0):
     return dq, dk, dv
 
 
+def _chunked(q, v):
+    """True if the library cuts this problem's sequence into chunks (few (batch, head) pairs) and d == e, i.e. when the
+    chunk states of one product can be handed to the product with k and v exchanged instead of being recomputed."""
+    b, h, n, d = q.shape
+    e = v.shape[-1]
+    return d == e and _lib.lib().lab200_la_plan_chunks(b * h, n, d, e) > 1
+
+
+def _fwd_keep(q, k, v, s):
+    """Forward that keeps its chunk states (KV prefixes, (e, d) per chunk) for the backward pass."""
+    o, _, handle = la_generic(q, k, v, s, keep_workspace=True)
+    return o, handle
+
+
+def _bwd_from_kept(q, k, v, s, do, handle):
+    """Backward in chunk mode with d == e: dq takes the forward's chunk states transposed, dv takes dk's; only dk's
+    (reverse-time sums of q^T do) are computed here."""
+    dq, _ = la_generic(do, v, k, s, resume_from=handle, resume_swapped=True, rebase=False)
+    dk, _, h2 = la_generic(v, do, q, s, reverse=True, keep_workspace=True)
+    dv, _ = la_generic(k, q, do, s, reverse=True, resume_from=h2, resume_swapped=True, rebase=False)
+    return dq, dk, dv
+
+
 def _check_inputs(q, k, v):
     _lib.require_cuda(q, k, v)
     if q.dim() != 4 or k.shape != q.shape or v.shape[:3] != q.shape[:3]:
@@ -127,7 +189,11 @@ class LightningAttention2(torch.autograd.Function):
         v = v.contiguous()
         s = s.contiguous()
         sl = _slopes_arg(s, q.shape[1], q.device)
-        o = _fwd(q, k, v, sl)
+        ctx.kept = None
+        if _chunked(q, v):
+            o, ctx.kept = _fwd_keep(q, k, v, s)
+        else:
+            o = _fwd(q, k, v, sl)
         ctx.save_for_backward(q, k, v, s)
         return o
 
@@ -135,6 +201,9 @@ class LightningAttention2(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, s = ctx.saved_tensors
         do = do.contiguous()
+        kept, ctx.kept = ctx.kept, None  # usable once: the transposed hand-over changes whose states they are
+        if kept is not None:
+            return _bwd_from_kept(q, k, v, s, do, kept) + (None,)
         sl = _slopes_arg(s, q.shape[1], q.device)
         dq, dk, dv = _bwd(q, k, v, sl, do)
         return dq, dk, dv, None
@@ -149,13 +218,20 @@ class LightningAttention2NoDecay(torch.autograd.Function):
         q = q.contiguous()
         k = k.contiguous()
         v = v.contiguous()
-        o = _fwd(q, k, v, None)
+        ctx.kept = None
+        if _chunked(q, v):
+            o, ctx.kept = _fwd_keep(q, k, v, None)
+        else:
+            o = _fwd(q, k, v, None)
         ctx.save_for_backward(q, k, v)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v = ctx.saved_tensors
+        kept, ctx.kept = ctx.kept, None
+        if kept is not None:
+            return _bwd_from_kept(q, k, v, None, do.contiguous(), kept)
         dq, dk, dv = _bwd(q, k, v, None, do.contiguous())
         return dq, dk, dv
 

@@ -334,3 +334,87 @@ def test_two_step_generic_call_reuses_chunk_states(cuda_lib, reverse, chunks):
     assert_parity(got, ref.float(), "two-step", False)
     _, st_loc2 = la_generic(None, bm, c, s, reverse=reverse, state_only=True, chunks=chunks)
     assert torch.equal(st_loc, st_loc2)
+
+
+@pytest.mark.parametrize("reverse", [False, True])
+@pytest.mark.parametrize("chunks", [1, 3])
+@pytest.mark.parametrize("d", [128, 48])
+def test_swapped_resume_reuses_transposed_chunk_states(cuda_lib, reverse, chunks, d):
+    """The chunk states of the product on (bm, c) serve the product on (c, bm) after an in-place transpose
+    (lab200_la_generic_resume_swapped): from a state-only call (incoming state still to be added) and from a resumed
+    call (incoming state already in)."""
+    torch.manual_seed(10)
+    b, h, n = 1, 3, 1536
+    a, bm, c, a2 = (torch.randn((b, h, n, d), device=DEV).bfloat16() for _ in range(4))
+    s = (la._build_slope_tensor(h).reshape(-1) * 0.02).to(DEV)
+    st_in = torch.randn((b, h, d, d), device=DEV)
+    st_in_t = st_in.transpose(2, 3).contiguous()
+    ref_swapped, _ = la_generic(a2, c, bm, s, reverse=reverse, state_in=st_in_t, chunks=chunks)
+    # state-only on (bm, c) -> swapped resume on (c, bm), which adds the incoming state itself
+    _, _, handle = la_generic(None, bm, c, s, reverse=reverse, state_only=True, chunks=chunks, keep_workspace=True)
+    got, _ = la_generic(a2, c, bm, s, reverse=reverse, state_in=st_in_t, chunks=chunks, resume_from=handle, resume_swapped=True)
+    assert_parity(got, ref_swapped.float(), "swapped-from-state-only", False)
+    # state-only -> resume on (bm, c) with the incoming state -> swapped resume on (c, bm) without adding it again
+    ref, _ = la_generic(a, bm, c, s, reverse=reverse, state_in=st_in, chunks=chunks)
+    _, _, handle = la_generic(None, bm, c, s, reverse=reverse, state_only=True, chunks=chunks, keep_workspace=True)
+    got, _, handle = la_generic(a, bm, c, s, reverse=reverse, state_in=st_in, chunks=chunks, resume_from=handle, keep_workspace=True)
+    assert_parity(got, ref.float(), "resumed", False)
+    got, _ = la_generic(a2, c, bm, s, reverse=reverse, state_in=st_in_t, chunks=chunks, resume_from=handle,
+                        resume_swapped=True, rebase=False)
+    assert_parity(got, ref_swapped.float(), "swapped-from-resumed", False)
+    with pytest.raises(RuntimeError):  # the handle now belongs to (c, bm)
+        la_generic(a2, c, bm, s, reverse=reverse, chunks=chunks, resume_from=handle, resume_swapped=True)
+
+
+@pytest.mark.parametrize("chunks", [0, 5])
+@pytest.mark.parametrize("d", [128, 64, 192])
+def test_chunked_backward_shares_chunk_states_between_dk_and_dv(cuda_lib, chunks, d):
+    """Few (batch, head) pairs and d == e: lab200_la2_bwd runs in chunk mode and dv takes dk's chunk states transposed."""
+    from lightning_attention_b200.ops.cuda.lightning_attn2 import _bwd, _fwd, _slopes_arg
+
+    b, h, n = 1, 4, 4096 + 128 * 3
+    q, k, v, do = make_inputs(b, h, n, d, d, torch.bfloat16, 1.0, seed=77)
+    s = (la._build_slope_tensor(h).reshape(-1) * 0.01).to(DEV)  # slow decay: the carried state matters everywhere
+    sl = _slopes_arg(s, h, q.device)
+    with torch.no_grad():
+        o = _fwd(q, k, v, sl, chunks=chunks)
+        dq, dk, dv = _bwd(q, k, v, sl, do, chunks=chunks)
+    compare_with_torch_reference(q, k, v, do, s, (o, dq, dk, dv), False, f"chunked-bwd-d{d}-c{chunks}")
+
+
+@pytest.mark.parametrize("x,y", [(128, 128), (48, 80), (16, 200)])
+@pytest.mark.parametrize("decay", [True, False])
+def test_combine_states_kernel_matches_formula(cuda_lib, x, y, decay):
+    """lab200_la_combine_states == the torch formula of distributed.combine_states, both layouts, every rank, both directions."""
+    from lightning_attention_b200 import distributed as D
+
+    torch.manual_seed(3)
+    R, b, h, L = 5, 2, 3, 256
+    gathered = torch.randn((R, b, h, x, y), device=DEV)
+    s = (la._build_slope_tensor(h).reshape(-1) * 0.01).to(DEV) if decay else None
+    dec = D._shard_decay(s, h, L, gathered.device)
+    for rank in range(R):
+        for reverse in (False, True):
+            ref = D.combine_states(gathered, dec, rank, reverse=reverse)
+            got, got_t = D.combine_gathered(gathered, s, L, rank, reverse=reverse)
+            assert torch.allclose(got, ref, rtol=1e-5, atol=1e-5), (rank, reverse)
+            assert torch.equal(got_t, got.transpose(2, 3).contiguous())
+
+
+@pytest.mark.parametrize("decay", [True, False])
+def test_autograd_in_chunk_mode_hands_chunk_states_from_forward_to_backward(cuda_lib, decay):
+    """Few (batch, head) pairs, d == e: the autograd Function keeps the forward's chunk states for dq and dk's for dv.
+    A second backward through the same graph (states already handed over) must give the same gradients."""
+    b, h, n, d = 1, 4, 4096 + 128 * 3, 128
+    assert cuda_lib.lab200_la_plan_chunks(b * h, n, d, d) > 1
+    q, k, v, do = make_inputs(b, h, n, d, d, torch.bfloat16, 1.0 if decay else 0.2, seed=78)
+    s = (la._build_slope_tensor(h).reshape(-1) * 0.01).to(DEV) if decay else None
+    o = la.lightning_attn_func(q, k, v, s)
+    o.backward(do, retain_graph=True)
+    first = tuple(t.grad.clone() for t in (q, k, v))
+    q.grad = k.grad = v.grad = None
+    o.backward(do)
+    second = (q.grad, k.grad, v.grad)
+    compare_with_torch_reference(q, k, v, do, s, (o.detach(),) + first, False, f"autograd-chunked-decay{decay}")
+    for x, y in zip(first, second):
+        assert_parity(x, y.float(), "second-backward", False)

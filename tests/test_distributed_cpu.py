@@ -21,9 +21,10 @@ def _free_port():
 
 
 def oracle_product(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0,
-                   keep_workspace=False, resume_from=None):
+                   keep_workspace=False, resume_from=None, resume_swapped=False, rebase=True):
     """Same call signature as the CUDA op `la_generic`, computed by the numpy oracle in fp64. The two-step protocol
-    (keep_workspace / resume_from) is honoured by handing back a token and checking that it comes back."""
+    (keep_workspace / resume_from / resume_swapped) is honoured by handing back a token that names the product it belongs
+    to and whether the incoming state is already in it, and checking the token that comes back."""
     from oracle import lightning_oracle as O
 
     f = lambda t: None if t is None else t.detach().double().numpy()
@@ -32,13 +33,17 @@ def oracle_product(a, bm, c, s=None, reverse=False, state_in=None, want_state=Fa
     out_t = None if state_only else torch.from_numpy(np.ascontiguousarray(out))
     st_t = torch.from_numpy(np.ascontiguousarray(st)).float().double()
     if resume_from is not None:
-        assert resume_from == ("handle", tuple(bm.shape), tuple(c.shape), bool(reverse))
+        tag, bshape, cshape, rev, based = resume_from
+        want = (tuple(c.shape), tuple(bm.shape)) if resume_swapped else (tuple(bm.shape), tuple(c.shape))
+        assert (tag, bshape, cshape, rev) == ("handle",) + want + (bool(reverse),)
+        assert based == (not rebase), "the incoming state must be added exactly once"
     if keep_workspace:
-        return out_t, st_t, ("handle", tuple(bm.shape), tuple(c.shape), bool(reverse))
+        based = (state_in is not None) or (resume_from is not None)
+        return out_t, st_t, ("handle", tuple(bm.shape), tuple(c.shape), bool(reverse), based)
     return out_t, st_t
 
 
-def _sp_worker(rank, world, port, scale, result_dir):
+def _sp_worker(rank, world, port, scale, result_dir, d=16, e=32):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -48,7 +53,7 @@ def _sp_worker(rank, world, port, scale, result_dir):
         from oracle import lightning_oracle as O
 
         torch.manual_seed(11)
-        b, h, L, d, e = 1, 3, 128, 16, 32
+        b, h, L = 1, 3, 128
         n = world * L
         q, k = (torch.randn(b, h, n, d, dtype=torch.float64) for _ in range(2))
         v, do = (torch.randn(b, h, n, e, dtype=torch.float64) for _ in range(2))
@@ -79,6 +84,16 @@ def test_sequence_parallel_matches_unsharded(tmp_path, world, scale):
         assert np.all(errs < 1e-4), (r, errs)
 
 
+def test_sequence_parallel_square_dims_reuse_transposed_states(tmp_path):
+    """d == e: dq resumes from the forward's kept chunk states and dv from dk's, both through the transposed hand-over;
+    the product stand-in checks every handle it is given (right product, incoming state added exactly once)."""
+    world = 2
+    mp.spawn(_sp_worker, args=(world, _free_port(), 1e-3, str(tmp_path), 32, 32), nprocs=world, join=True)
+    for r in range(world):
+        errs = np.load(tmp_path / f"err_{r}.npy")
+        assert np.all(errs < 1e-4), (r, errs)
+
+
 def _fail_worker(rank, world, port, result_dir):
     """Rank 1 raises before the exchange; rank 0's all-gather must end with an error (short timeout), not hang."""
     import datetime
@@ -93,7 +108,7 @@ def _fail_worker(rank, world, port, result_dir):
     try:
         if rank == 1:
             raise ValueError("injected host-side failure before the state exchange")
-        D.exchange_states(torch.zeros(1, 2, 4, 4))
+        D.gather_states(torch.zeros(1, 2, 4, 4))
     except ValueError:
         outcome = "raised"
     except Exception:
