@@ -235,6 +235,49 @@ def run_sweep(emit):
                           "fwd_gbs": 4.0 * elems / fwd / 1e6, "bwd_gbs": 6.0 * elems / bwd / 1e6}))
 
 
+TRACE_SLOTS = ["mma: block start", "mma: X issued", "mma: P and C ready", "mma: D issued", "mask: S ready", "mask: P written",
+               "state: Bm scaled", "state: PC+D done seen", "state: D drained", "state: next state ready", "state: accumulators free",
+               "state: output tile staged"]
+
+
+def run_trace(emit):
+    """In-kernel clock trace of the attention block kernel (lab200_la_debug_trace): one forward-time and one reverse-time
+    launch at b4 h32 d=e=128, n = --n; CTA (0,0,0) stamps clock64() at twelve hand-over points of every 128-token block.
+    Prints one JSON line per direction: the block period and each point's mean offset from the MMA warp's block start,
+    in SM cycles, over the steady-state blocks."""
+    import torch
+
+    import lightning_attention_b200 as la
+    from lightning_attention_b200 import _lib
+    from lightning_attention_b200.ops.cuda.lightning_attn2 import la_generic
+
+    if not torch.cuda.is_available():
+        raise SystemExit("--trace needs a CUDA GPU")
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED)
+    a, bm, c = (torch.randn((B, H, N_TOK, D), device=dev, generator=g).to(torch.bfloat16) for _ in range(3))
+    s = la._build_slope_tensor(H).to(dev)
+    nb = N_TOK // 128
+    for reverse in (False, True):
+        for _ in range(3):
+            la_generic(a, bm, c, s, reverse=reverse, chunks=1)
+        torch.cuda.synchronize()
+        tr = torch.zeros(nb * 16, dtype=torch.int64, device=dev)
+        L.lab200_la_debug_trace(tr.data_ptr(), nb)
+        la_generic(a, bm, c, s, reverse=reverse, chunks=1)
+        torch.cuda.synchronize()
+        L.lab200_la_debug_trace(None, 0)
+        t = tr.view(nb, 16).cpu()
+        lo, hi = min(8, nb // 2), max(nb - 2, nb // 2 + 1)
+        rel = (t - t[:, 0:1])[lo:hi].double().mean(0).tolist()
+        period = (t[1:, 0] - t[:-1, 0])[lo:hi].double().mean().item()
+        emit(json.dumps({"trace": "la_pipe_kernel", "direction": "reverse-time" if reverse else "forward-time",
+                         "shape": [B, H, N_TOK, D], "blocks_averaged": hi - lo, "block_period_cycles": round(period),
+                         "offsets_cycles": {name: round(x) for name, x in zip(TRACE_SLOTS, rel)}}))
+
+
 def main():
     global N_TOK
     # Libraries (NCCL's version banner, for one) print to file descriptor 1; the contract is ONE JSON line on stdout.
@@ -255,6 +298,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--n", type=int, default=N_TOK, help="sequence length (default: the benchmark's largest point)")
+    ap.add_argument("--trace", action="store_true",
+                    help="print the in-kernel clock trace of the attention block kernel (one JSON line per direction) and exit")
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the single bench line, print one JSON line per point of the reference's benchmark "
                          "tables (Lightning2 / NoDecay fwd and bwd over n; SRMSNorm fwd and bwd over n) and exit")
@@ -271,6 +316,9 @@ def main():
         return
     if args.sweep:
         run_sweep(emit)
+        return
+    if args.trace:
+        run_trace(emit)
         return
 
     import torch
