@@ -272,6 +272,11 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       float g[32];  // per-column part of the decay inside a live tile: lambda^i (reverse) or lambda^(31-i) (forward)
 #pragma unroll
       for (int i = 0; i < 32; ++i) g[i] = ex2f(s2 * static_cast<float>(reverse ? i : 31 - i));
+      // Diagonal tile: lambda^(lane-i) = g[i] * lambda^(lane-31) (forward), lambda^(i-lane) = g[i] * lambda^(-lane) (reverse).
+      // The row factor is >= 1 here, at most lambda^-31; for decay rates where that could leave the fp32 range the
+      // per-element table is used instead (CTA-uniform choice).
+      const bool diag_rank1 = s * 31.f < 60.f;
+      const float rowd = diag_rank1 ? ex2f(s2 * static_cast<float>(reverse ? -lane : lane - 31)) : 0.f;
       for (int it = 0; it < nb; ++it) {
         const int st = it & 1;
         const uint32_t par = (it >> 1) & 1;
@@ -298,6 +303,17 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 32; i += 2)
               pk[i >> 1] = pack2<FMT>(__uint_as_float(v[0][i]) * (rowf * g[i]), __uint_as_float(v[0][i + 1]) * (rowf * g[i + 1]));
+          } else if (kind == 2 && diag_rank1) {
+            float rd = rowd;
+            asm volatile("" : "+f"(rd));  // keeps the 32 products rd * g[i] from being hoisted out of the block loop into registers
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const int d0 = reverse ? (i - lane) : (lane - i);
+              const int d1 = reverse ? (d0 + 1) : (d0 - 1);
+              const float f0 = (d0 >= 0) ? __uint_as_float(v[0][i]) * (rd * g[i]) : 0.f;
+              const float f1 = (d1 >= 0) ? __uint_as_float(v[0][i + 1]) * (rd * g[i + 1]) : 0.f;
+              pk[i >> 1] = pack2<FMT>(f0, f1);
+            }
           } else if (kind == 2) {
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
