@@ -133,7 +133,7 @@ int launch_tiled(int nks, int nvs, const CUtensorMap& tA, const CUtensorMap& tB,
 int smem_bytes_pipe(int nks, int nvs, int mode) {
   const int slab = LA_SLAB_BYTES;
   int b = 2 * nks * slab + 4 * slab;
-  if (mode == 0) b += 2 * nks * slab + nks * nvs * 64 * 128;
+  if (mode == 0) b += 2 * (nks > nvs ? nks : nvs) * slab + nks * nvs * 64 * 128;  // A stages also stage the output tile
   return b + 2 * LAP_NUM_BARS * 8 + 16 + 512 + 1024;  // barriers, flags, decay table, alignment slack
 }
 

@@ -24,7 +24,7 @@ constexpr int LAP_MASK_THREADS = 128, LAP_STATE_THREADS = 256;
 
 
 // barrier slots (each has two instances, indexed by block parity)
-enum : int { LAP_FULL_AB = 0, LAP_FULL_C, LAP_S_READY, LAP_P_READY, LAP_A_FREE, LAP_PCD_DONE, LAP_O_FREE, LAP_D_FREE,
+enum : int { LAP_FULL_A = 0, LAP_FULL_BC, LAP_S_READY, LAP_P_READY, LAP_PC_DONE, LAP_D_DONE, LAP_O_FREE, LAP_D_FREE,
              LAP_STATE_READY, LAP_O_STAGED, LAP_BM_SCALED, LAP_NUM_BARS };
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -70,6 +70,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int DKP = 64 * NKS;
   constexpr int SC = DKP / 2;
   constexpr int OC = DV / 2;
+  constexpr int NAS = NKS > NVS ? NKS : NVS;  // slabs per A stage: the stage also stages the block's output tile
   constexpr uint32_t T_S = 0, T_OI = 128, T_OX = 128 + DV, T_D = 128 + 2 * DV;
   static_assert(T_D + DKP <= 512, "TMEM budget");
   constexpr uint32_t IDESC_S = umma_idesc(FMT, 128, 128, 0, 0);
@@ -80,11 +81,11 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t sA = base;                                         // 2 stages x NKS slabs (MODE 0)
-  const uint32_t sB = sA + (MODE == 0 ? 2 * NKS * SLAB : 0);        // 2 stages x NKS slabs
+  const uint32_t sA = base;                                         // 2 stages x NAS slabs (MODE 0)
+  const uint32_t sB = sA + (MODE == 0 ? 2 * NAS * SLAB : 0);        // 2 stages x NKS slabs
   const uint32_t sC = sB + 2 * NKS * SLAB;                          // 2 stages x 2 slabs
   const uint32_t sS = sC + 2 * 2 * SLAB;                            // bf16 state, NKS x [DV rows][128 B] (MODE 0)
-  // Output tiles are staged in the C stage of their own block (free once PC and D are done) and leave by TMA store.
+  // Output tiles are staged in the A stage of their own block (free once S and X are done) and leave by TMA store.
   const uint32_t sBar = sS + (MODE == 0 ? NKS * DV * 128 : 0);      // 2 x LAP_NUM_BARS mbarriers
   const uint32_t sMisc = sBar + 2 * LAP_NUM_BARS * 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sMisc - raw));
@@ -141,8 +142,8 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     // =========================================== TMA producer ===========================================
-    // Also issues the TMA stores of the output tiles: a tile is staged in the C stage of its block, and that stage
-    // is reloaded (for block it+2) only after the store has read it.
+    // Also issues the TMA stores of the output tiles: a tile is staged in the A stage of its block (S and X are done
+    // with A by the time P C has run), and that stage is reloaded (for block it+2) only after the store has read it.
     if (lane == 0) {
       auto blk_of = [&](int i) { return reverse ? (blk_end - 1 - i) : (blk_begin + i); };
       auto store_tile = [&](int i) -> bool {  // output tile of block i: wait until it is staged, then store it
@@ -150,7 +151,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!lap_wait(bar(LAP_O_STAGED, sst), (i >> 1) & 1, abort_flag, budget)) return false;
 #pragma unroll
         for (int vs = 0; vs < NVS; ++vs)
-          tma_store_3d(&tmO, sC + (sst * 2 + vs) * SLAB, dv_off + vs * 64, blk_of(i) * LA_BLOCK, bh);
+          tma_store_3d(&tmO, sA + (sst * NAS + vs) * SLAB, dv_off + vs * 64, blk_of(i) * LA_BLOCK, bh);
         tma_store_commit();
         return true;
       };
@@ -159,29 +160,26 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int blk = blk_of(it);
         const int st = it & 1;
         const uint32_t prev_par = ((it >> 1) & 1) ^ 1;  // parity of the previous use of this stage (block it-2)
-        if (it >= 2) {
-          // stage reuse: block it-2 must be done with A (S, X) and with Bm (D)
-          if (MODE == 0 && !lap_wait(bar(LAP_A_FREE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
-          if (!lap_wait(bar(LAP_PCD_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
-        }
-        mbar_arrive_expect_tx(bar(LAP_FULL_AB, st), (MODE == 0 ? 2 : 1) * NKS * SLAB);
         if (MODE == 0) {
+          if (it >= 2) {
+            // the A stage holds the staged output tile of block it-2: store it and wait until it has been read
+            if (!store_tile(it - 2)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
+            tma_store_wait_read();
+          }
+          mbar_arrive_expect_tx(bar(LAP_FULL_A, st), NKS * SLAB);
 #pragma unroll
           for (int ks = 0; ks < NKS; ++ks)
-            tma_load_3d(sA + (st * NKS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_AB, st));
+            tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_A, st));
         }
+        // Bm and C of block it-2 are read last by D_{it-2}
+        if (it >= 2 && !lap_wait(bar(LAP_D_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
+        mbar_arrive_expect_tx(bar(LAP_FULL_BC, st), (NKS + 2) * SLAB);
 #pragma unroll
         for (int ks = 0; ks < NKS; ++ks)
-          tma_load_3d(sB + (st * NKS + ks) * SLAB, &tmB, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_AB, st));
-        if (MODE == 0 && it >= 2) {
-          // the C stage still holds the staged output tile of block it-2: store it and wait until it has been read
-          if (!store_tile(it - 2)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
-          tma_store_wait_read();
-        }
-        mbar_arrive_expect_tx(bar(LAP_FULL_C, st), 2 * SLAB);
+          tma_load_3d(sB + (st * NKS + ks) * SLAB, &tmB, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_BC, st));
 #pragma unroll
         for (int vs = 0; vs < 2; ++vs)
-          tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_C, st));
+          tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_BC, st));
       }
       if (MODE == 0 && alive && *abort_flag == 0) {
         for (int i = max(nb - 2, 0); i < nb; ++i) {
@@ -194,13 +192,15 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ============================================ MMA issuer ============================================
     // Issue order per block: X_i, PC_i, S_{i+1}, D_i. S_{i+1} goes out before D_i so that the mask group can
     // start on the next block while the state MMA of this one still runs (the tensor pipe executes in issue order,
-    // so S_{i+1}, which overwrites the TMEM columns P_i lives in, cannot overtake PC_i).
+    // so S_{i+1}, which overwrites the TMEM columns P_i lives in, cannot overtake PC_i). P C commits to its own
+    // barrier: the output tile leaves TMEM while S_{i+1} and D_i run, and only the state update waits for D_i.
     if (lane == 0) {
       auto issue_S = [&](int i) -> bool {
         const int ist = i & 1;
-        if (!lap_wait(bar(LAP_FULL_AB, ist), (i >> 1) & 1, abort_flag, budget)) return false;
+        if (!lap_wait(bar(LAP_FULL_A, ist), (i >> 1) & 1, abort_flag, budget)) return false;
+        if (!lap_wait(bar(LAP_FULL_BC, ist), (i >> 1) & 1, abort_flag, budget)) return false;
         tc_fence_after_sync();
-        const uint32_t a0 = sA + ist * NKS * SLAB, b0 = sB + ist * NKS * SLAB;
+        const uint32_t a0 = sA + ist * NAS * SLAB, b0 = sB + ist * NKS * SLAB;
         for (int kq = 0; kq < nk16; ++kq) {  // S = A Bm^T
           const uint32_t off = (kq >> 2) * SLAB + (kq & 3) * 32;
           umma_f16(tmem + T_S, smem_desc_sw128(a0 + off, 16), smem_desc_sw128(b0 + off, 16), IDESC_S, kq > 0);
@@ -218,7 +218,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t par = (it >> 1) & 1;
         const int pst = st ^ 1;                         // instance used by block it-1
         const uint32_t ppar = ((it - 1) >> 1) & 1;      // and its parity
-        const uint32_t sAs = sA + st * NKS * SLAB, sBs = sB + st * NKS * SLAB, sCs = sC + st * 2 * SLAB;
+        const uint32_t sAs = sA + st * NAS * SLAB, sBs = sB + st * NKS * SLAB, sCs = sC + st * 2 * SLAB;
         const bool have_state = have_state_in || (it > 0);
         LAP_TRACE(0, it)
         if (MODE == 0) {
@@ -232,22 +232,20 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               umma_f16(tmem + T_OX, smem_desc_sw128(sAs + offA, 16), smem_desc_sw128(sS + offS, 16), IDESC_X, kq > 0);
             }
           }
-          umma_commit(bar(LAP_A_FREE, st));  // S_it and X_it are done with A (and X_it with the bf16 state)
           LAP_TRACE(1, it)
           if (!lap_wait(bar(LAP_P_READY, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         }
-        if (!lap_wait(bar(LAP_FULL_C, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
+        if (!lap_wait(bar(LAP_FULL_BC, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
         LAP_TRACE(2, it)
         tc_fence_after_sync();
         if (MODE == 0) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)  // O_intra = P C, P read from TMEM
             umma_f16_ts(tmem + T_OI, tmem + T_S + kk * 8, smem_desc_sw128(sCs + kk * 2048, SLAB), IDESC_PC, kk > 0);
+          umma_commit(bar(LAP_PC_DONE, st));  // O_intra and O_inter of this block are complete; S_it, X_it are done with A
           if (it + 1 < nb) {
             if (!issue_S(it + 1)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
           }
-        } else {
-          if (!lap_wait(bar(LAP_FULL_AB, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
         }
         if (!lap_wait(bar(LAP_BM_SCALED, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         if (it > 0 && !lap_wait(bar(LAP_D_FREE, pst), ppar, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
@@ -255,7 +253,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // local StateT = C^T (w_state Bm)
           umma_f16(tmem + T_D, smem_desc_sw128(sCs + kk * 2048, SLAB), smem_desc_sw128(sBs + kk * 2048, SLAB), IDESC_ST, kk > 0);
-        umma_commit(bar(LAP_PCD_DONE, st));
+        umma_commit(bar(LAP_D_DONE, st));
         LAP_TRACE(3, it)
       }
     }
@@ -390,7 +388,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // ---- Bm rows *= w_state(r), in place, for D_it: this thread's half of the row's 16-byte chunks ----------
       {
         // S_it must be done with the unscaled tile (state-only mode: the tile must have landed)
-        bool ok = lap_wait(bar(MODE == 0 ? LAP_S_READY : LAP_FULL_AB, st), par, abort_flag, budget);
+        bool ok = lap_wait(bar(MODE == 0 ? LAP_S_READY : LAP_FULL_BC, st), par, abort_flag, budget);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
         if (s != 0.f) {
@@ -417,41 +415,15 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_arrive(bar(LAP_BM_SCALED, st));
         if (store_thread) { LAP_TRACE(6, it) }
       }
-      {
-        bool ok = lap_wait(bar(LAP_PCD_DONE, st), par, abort_flag, budget);
+      if (MODE == 0) {
+        // ---- output tile: TMEM -> registers -> swizzled shared-memory slabs -> TMA store. Runs while S_{it+1} and
+        //      D_it are still in the tensor pipe. --------------------------------------------------------------
+        bool ok = lap_wait(bar(LAP_PC_DONE, st), par, abort_flag, budget);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
-      }
-      if (store_thread) { LAP_TRACE(7, it) }
-      tc_fence_after_sync();
-      // ---- state recurrence --------------------------------------------------------------------------
-      if (q * 32 < DV) {
-#pragma unroll
-        for (int cc = 0; cc < SC; cc += 32) {
-          uint32_t dl[32];
-          tmem_ld32(tmem + lanebase + T_D + hf * SC + cc, dl);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) stt[cc + i] = fmaf(decay_blk, stt[cc + i], __uint_as_float(dl[i]));
-        }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(bar(LAP_D_FREE, st));
-      if (store_thread) { LAP_TRACE(8, it) }
-      if (MODE == 0) {
-        // X_it (and S_it) have read A and the old bf16 state: both may be overwritten now, and O_inter is complete
-        bool ok = lap_wait(bar(LAP_A_FREE, st), par, abort_flag, budget);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
+        if (store_thread) { LAP_TRACE(7, it) }
         tc_fence_after_sync();
-        if (has_next) {
-          store_state_smem();
-          fence_proxy_async_smem();
-          mbar_arrive(bar(LAP_STATE_READY, st ^ 1));  // state entering block it+1
-        }
-        if (store_thread) { LAP_TRACE(9, it) }
-        // ---- output tile: TMEM -> registers -> swizzled shared-memory slabs -> TMA store --------------------
-        const uint32_t sOs = sC + st * 2 * SLAB;  // PC_it and D_it are done with this C stage
+        const uint32_t sOs = sA + st * NAS * SLAB;  // S_it and X_it are done with this A stage
 #pragma unroll
         for (int cc = 0; cc < OC; cc += 16) {
           uint32_t a[16], b[16];
@@ -483,6 +455,33 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_arrive(bar(LAP_O_STAGED, st));  // the producer warp stores the tile
         if (store_thread) { LAP_TRACE(11, it) }
       }
+      {
+        bool ok = lap_wait(bar(LAP_D_DONE, st), par, abort_flag, budget);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
+      }
+      if (store_thread) { LAP_TRACE(8, it) }
+      tc_fence_after_sync();
+      // ---- state recurrence --------------------------------------------------------------------------
+      if (q * 32 < DV) {
+#pragma unroll
+        for (int cc = 0; cc < SC; cc += 32) {
+          uint32_t dl[32];
+          tmem_ld32(tmem + lanebase + T_D + hf * SC + cc, dl);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) stt[cc + i] = fmaf(decay_blk, stt[cc + i], __uint_as_float(dl[i]));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar(LAP_D_FREE, st));
+      if (MODE == 0 && has_next) {
+        // X_it finished before P C did, so the old bf16 copy of the state may be overwritten
+        store_state_smem();
+        fence_proxy_async_smem();
+        mbar_arrive(bar(LAP_STATE_READY, st ^ 1));  // state entering block it+1
+      }
+      if (store_thread) { LAP_TRACE(9, it) }
     }
     if (*abort_flag == 0 && p.state_out != nullptr && st_row_valid) {
       float* dst = p.state_out +
