@@ -6,7 +6,7 @@
 // at the same time and hand tiles to each other through mbarriers:
 //
 //   warp 0      TMA producer   loads A, Bm, C tiles of block i+1, i+2 into two shared-memory stages
-//   warp 1      MMA issuer     S_i = A Bm^T, X_i = A State_i, PC_i = P_i C, D_i = C^T (w Bm)   (one thread)
+//   warp 1      MMA issuer     X_i = A State_i, D_i = C^T (w Bm), PC_i = P_i C, S_{i+1} = A Bm^T, in this order (one thread)
 //   warps 2-5   mask group     S_i (TMEM) -> decay mask -> P_i (bf16, back into TMEM over S)
 //   warps 6-13  state/output   Bm_i rows *= w_state (for D_i); D_i -> StateT = lambda^128 StateT + D_i (fp32 registers)
 //                              -> bf16 copy for X_{i+1}; O_i = PC_i + w_out X_i -> swizzled shared-memory tile -> TMA store
@@ -162,17 +162,13 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t prev_par = ((it >> 1) & 1) ^ 1;  // parity of the previous use of this stage (block it-2)
         if (MODE == 0) {
           if (it >= 2) {
-            // the A stage holds the staged output tile of block it-2: store it and wait until it has been read
+            // A staged output tile means P C of block it-2 has run, the last MMA to touch that block's A, Bm and C.
+            // The A stage holds the tile: store it; Bm and C can be reloaded at once, A when the store has read the tile.
             if (!store_tile(it - 2)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
-            tma_store_wait_read();
           }
-          mbar_arrive_expect_tx(bar(LAP_FULL_A, st), NKS * SLAB);
-#pragma unroll
-          for (int ks = 0; ks < NKS; ++ks)
-            tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_A, st));
+        } else if (it >= 2) {
+          if (!lap_wait(bar(LAP_D_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         }
-        // Bm and C of block it-2 are read last by D_{it-2}
-        if (it >= 2 && !lap_wait(bar(LAP_D_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         mbar_arrive_expect_tx(bar(LAP_FULL_BC, st), (NKS + 2) * SLAB);
 #pragma unroll
         for (int ks = 0; ks < NKS; ++ks)
@@ -180,6 +176,13 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
         for (int vs = 0; vs < 2; ++vs)
           tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_BC, st));
+        if (MODE == 0) {
+          if (it >= 2) tma_store_wait_read();
+          mbar_arrive_expect_tx(bar(LAP_FULL_A, st), NKS * SLAB);
+#pragma unroll
+          for (int ks = 0; ks < NKS; ++ks)
+            tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_A, st));
+        }
       }
       if (MODE == 0 && alive && *abort_flag == 0) {
         for (int i = max(nb - 2, 0); i < nb; ++i) {
@@ -190,10 +193,11 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ============================================ MMA issuer ============================================
-    // Issue order per block: X_i, PC_i, S_{i+1}, D_i. S_{i+1} goes out before D_i so that the mask group can
-    // start on the next block while the state MMA of this one still runs (the tensor pipe executes in issue order,
-    // so S_{i+1}, which overwrites the TMEM columns P_i lives in, cannot overtake PC_i). P C commits to its own
-    // barrier: the output tile leaves TMEM while S_{i+1} and D_i run, and only the state update waits for D_i.
+    // Issue order per block: X_i, D_i, PC_i, S_{i+1}. X_i and D_i need nothing from the mask group, so they run while
+    // it turns S_i into P_i; D_i this early also means the next state is ready long before X_{i+1} asks for it.
+    // S_{i+1} overwrites the TMEM columns P_i lives in, so it follows PC_i (the tensor pipe executes in issue order).
+    // D and P C commit to their own barriers: the state update starts after D_i, the output tile leaves TMEM after
+    // PC_i while S_{i+1}, X_{i+1} and D_{i+1} run.
     if (lane == 0) {
       auto issue_S = [&](int i) -> bool {
         const int ist = i & 1;
@@ -233,28 +237,28 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
           LAP_TRACE(1, it)
-          if (!lap_wait(bar(LAP_P_READY, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         }
-        if (!lap_wait(bar(LAP_FULL_BC, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
-        LAP_TRACE(2, it)
-        tc_fence_after_sync();
-        if (MODE == 0) {
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)  // O_intra = P C, P read from TMEM
-            umma_f16_ts(tmem + T_OI, tmem + T_S + kk * 8, smem_desc_sw128(sCs + kk * 2048, SLAB), IDESC_PC, kk > 0);
-          umma_commit(bar(LAP_PC_DONE, st));  // O_intra and O_inter of this block are complete; S_it, X_it are done with A
-          if (it + 1 < nb) {
-            if (!issue_S(it + 1)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
-          }
-        }
+        if (MODE != 0 && !lap_wait(bar(LAP_FULL_BC, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
         if (!lap_wait(bar(LAP_BM_SCALED, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         if (it > 0 && !lap_wait(bar(LAP_D_FREE, pst), ppar, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // local StateT = C^T (w_state Bm)
           umma_f16(tmem + T_D, smem_desc_sw128(sCs + kk * 2048, SLAB), smem_desc_sw128(sBs + kk * 2048, SLAB), IDESC_ST, kk > 0);
-        umma_commit(bar(LAP_D_DONE, st));
+        umma_commit(bar(LAP_D_DONE, st));  // also: X_it is done with the bf16 state copy
         LAP_TRACE(3, it)
+        if (MODE == 0) {
+          if (!lap_wait(bar(LAP_P_READY, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
+          LAP_TRACE(2, it)
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)  // O_intra = P C, P read from TMEM
+            umma_f16_ts(tmem + T_OI, tmem + T_S + kk * 8, smem_desc_sw128(sCs + kk * 2048, SLAB), IDESC_PC, kk > 0);
+          umma_commit(bar(LAP_PC_DONE, st));  // O_intra and O_inter are complete; nothing reads A, Bm, C of this block any more
+          if (it + 1 < nb) {
+            if (!issue_S(it + 1)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
+          }
+        }
       }
     }
   } else if (warp < 6) {
@@ -380,44 +384,81 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_arrive(bar(LAP_STATE_READY, 0));  // state entering block 0
     }
 
-    for (int it = 0; it < nb; ++it) {
+    // Bm rows of block j *= w_state(r), in place, for D_j: this thread's half of the row's 16-byte chunks.
+    auto scale_bm = [&](int j) -> bool {
+      const int st = j & 1;
+      // S_j must be done with the unscaled tile (state-only mode: the tile must have landed)
+      bool ok = lap_wait(bar(MODE == 0 ? LAP_S_READY : LAP_FULL_BC, st), (j >> 1) & 1, abort_flag, budget);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return false;
+      if (s != 0.f) {
+        constexpr int NCH = NKS * 4;  // chunks per thread
+        const uint32_t sBs = sB + st * NKS * SLAB;
+        uint32_t u[NCH][4];
+        uint32_t addr[NCH];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int gch = hf * NCH + c;  // chunk index in the row, 0 .. NKS*8-1
+          const int ks = gch >> 3, p0 = gch & 7;
+          const int pos = (NCH >= 8) ? ((p0 + r) & 7) : ((p0 & 4) | ((p0 + r) & 3));  // spread the warp over the banks
+          addr[c] = sBs + ks * SLAB + r * 128 + (pos << 4);
+          ld_shared_v4(addr[c], u[c][0], u[c][1], u[c][2], u[c][3]);
+        }
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+          for (int j2 = 0; j2 < 4; ++j2) u[c][j2] = mul2<FMT>(u[c][j2], w_state2);
+          st_shared_v4(addr[c], u[c][0], u[c][1], u[c][2], u[c][3]);
+        }
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(bar(LAP_BM_SCALED, st));
+      if (store_thread) { LAP_TRACE(6, j) }
+      return true;
+    };
+    // Order of work per block it: state update (after D_it), output tile (after PC_it), Bm scaling for block it+1
+    // (after S_{it+1}) - the order in which the MMA warp completes them.
+    bool live = true;
+    if (MODE == 0 && nb > 0) {
+      live = scale_bm(0);
+      if (!live) LAP_FAIL(LA_ERR_WAIT_MMA1)
+    }
+    for (int it = 0; it < nb && live; ++it) {
       const int st = it & 1;
       const uint32_t par = (it >> 1) & 1;
       const bool has_next = (it + 1 < nb);
       const bool have_state = have_state_in || (it > 0);
-      // ---- Bm rows *= w_state(r), in place, for D_it: this thread's half of the row's 16-byte chunks ----------
+      if (MODE != 0 && !scale_bm(it)) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
       {
-        // S_it must be done with the unscaled tile (state-only mode: the tile must have landed)
-        bool ok = lap_wait(bar(MODE == 0 ? LAP_S_READY : LAP_FULL_BC, st), par, abort_flag, budget);
+        bool ok = lap_wait(bar(LAP_D_DONE, st), par, abort_flag, budget);
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
-        if (s != 0.f) {
-          constexpr int NCH = NKS * 4;  // chunks per thread
-          const uint32_t sBs = sB + st * NKS * SLAB;
-          uint32_t u[NCH][4];
-          uint32_t addr[NCH];
-#pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            const int gch = hf * NCH + c;  // chunk index in the row, 0 .. NKS*8-1
-            const int ks = gch >> 3, p0 = gch & 7;
-            const int pos = (NCH >= 8) ? ((p0 + r) & 7) : ((p0 & 4) | ((p0 + r) & 3));  // spread the warp over the banks
-            addr[c] = sBs + ks * SLAB + r * 128 + (pos << 4);
-            ld_shared_v4(addr[c], u[c][0], u[c][1], u[c][2], u[c][3]);
-          }
-#pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) u[c][j] = mul2<FMT>(u[c][j], w_state2);
-            st_shared_v4(addr[c], u[c][0], u[c][1], u[c][2], u[c][3]);
-          }
-          fence_proxy_async_smem();
-        }
-        mbar_arrive(bar(LAP_BM_SCALED, st));
-        if (store_thread) { LAP_TRACE(6, it) }
+        if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
       }
+      if (store_thread) { LAP_TRACE(8, it) }
+      tc_fence_after_sync();
+      // ---- state recurrence --------------------------------------------------------------------------
+      if (q * 32 < DV) {
+#pragma unroll
+        for (int cc = 0; cc < SC; cc += 32) {
+          uint32_t dl[32];
+          tmem_ld32(tmem + lanebase + T_D + hf * SC + cc, dl);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) stt[cc + i] = fmaf(decay_blk, stt[cc + i], __uint_as_float(dl[i]));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar(LAP_D_FREE, st));
+      if (MODE == 0 && has_next) {
+        // X_it was issued before D_it, so it is done with the old bf16 copy of the state
+        store_state_smem();
+        fence_proxy_async_smem();
+        mbar_arrive(bar(LAP_STATE_READY, st ^ 1));  // state entering block it+1
+      }
+      if (store_thread) { LAP_TRACE(9, it) }
       if (MODE == 0) {
-        // ---- output tile: TMEM -> registers -> swizzled shared-memory slabs -> TMA store. Runs while S_{it+1} and
-        //      D_it are still in the tensor pipe. --------------------------------------------------------------
+        // ---- output tile: TMEM -> registers -> swizzled shared-memory slabs -> TMA store. Runs while S_{it+1},
+        //      X_{it+1} and D_{it+1} are in the tensor pipe. --------------------------------------------------------------
         bool ok = lap_wait(bar(LAP_PC_DONE, st), par, abort_flag, budget);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
@@ -455,33 +496,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_arrive(bar(LAP_O_STAGED, st));  // the producer warp stores the tile
         if (store_thread) { LAP_TRACE(11, it) }
       }
-      {
-        bool ok = lap_wait(bar(LAP_D_DONE, st), par, abort_flag, budget);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
-      }
-      if (store_thread) { LAP_TRACE(8, it) }
-      tc_fence_after_sync();
-      // ---- state recurrence --------------------------------------------------------------------------
-      if (q * 32 < DV) {
-#pragma unroll
-        for (int cc = 0; cc < SC; cc += 32) {
-          uint32_t dl[32];
-          tmem_ld32(tmem + lanebase + T_D + hf * SC + cc, dl);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) stt[cc + i] = fmaf(decay_blk, stt[cc + i], __uint_as_float(dl[i]));
-        }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(bar(LAP_D_FREE, st));
-      if (MODE == 0 && has_next) {
-        // X_it finished before P C did, so the old bf16 copy of the state may be overwritten
-        store_state_smem();
-        fence_proxy_async_smem();
-        mbar_arrive(bar(LAP_STATE_READY, st ^ 1));  // state entering block it+1
-      }
-      if (store_thread) { LAP_TRACE(9, it) }
+      if (MODE == 0 && has_next && !scale_bm(it + 1)) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
     }
     if (*abort_flag == 0 && p.state_out != nullptr && st_row_valid) {
       float* dst = p.state_out +
