@@ -394,7 +394,9 @@ def main():
         x = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g).requires_grad_()
         dy = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g)
         norm = la.SimpleRMSNorm(Nf)
-        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        # 1 GiB: flushes L2 and keeps the GPU busy long enough for the host to enqueue forward and backward behind it,
+        # so the events bracket device time, not the autograd engine's launch latency
+        flush = torch.empty(1024 * 1024 * 1024, dtype=torch.uint8, device=dev)
         tf, tb = [], []
         for i in range(8):
             x.grad = None
@@ -406,7 +408,7 @@ def main():
                 tf.append(a.elapsed_time(b_)); tb.append(b_.elapsed_time(c))
         fms, bms = statistics.median(tf), statistics.median(tb)
         srms = {"shape": [M, Nf], "fwd_ms": fms, "bwd_ms": bms, "fwd_gbs": 4.0 * M * Nf / fms / 1e6,
-                "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API incl. autograd overhead; L2 flushed between reps"}
+                "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API (autograd Function); L2 flushed between reps by a 1 GiB memset the launches queue behind"}
         del x, dy, flush
 
     # ---- long-context leg: b=1, h=32, d=e=128, 131072 tokens per GPU (the sequence-parallel shard size) ----
