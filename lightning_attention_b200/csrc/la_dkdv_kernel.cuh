@@ -251,6 +251,10 @@ la_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     float g[32];  // per-column part of the decay inside a live tile: lambda^i
 #pragma unroll
     for (int i = 0; i < 32; ++i) g[i] = ex2f(s2 * static_cast<float>(i));
+    // Diagonal tile: lambda^(i-lane) = g[i] * lambda^(-lane); the row factor is >= 1, at most lambda^-31, and the per-element
+    // table is used instead for decay rates where it could leave the fp32 range (CTA-uniform choice).
+    const bool diag_rank1 = s * 31.f < 60.f;
+    const float rowd = diag_rank1 ? ex2f(-s2 * static_cast<float>(lane)) : 0.f;
     bool alive = true;
     for (int it = 0; it < nb && alive; ++it) {
 #pragma unroll 1
@@ -275,6 +279,16 @@ la_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 32; i += 2)
               pk[i >> 1] = pack2<FMT>(__uint_as_float(v[i]) * (rowf * g[i]), __uint_as_float(v[i + 1]) * (rowf * g[i + 1]));
+          } else if (kind == 2 && diag_rank1) {
+            float rd = rowd;
+            asm volatile("" : "+f"(rd));  // keeps the 32 products rd * g[i] from being hoisted out of the block loop into registers
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const int d0 = i - lane, d1 = d0 + 1;
+              const float f0 = (d0 >= 0) ? __uint_as_float(v[i]) * (rd * g[i]) : 0.f;
+              const float f1 = (d1 >= 0) ? __uint_as_float(v[i + 1]) * (rd * g[i + 1]) : 0.f;
+              pk[i >> 1] = pack2<FMT>(f0, f1);
+            }
           } else if (kind == 2) {
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
