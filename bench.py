@@ -411,6 +411,29 @@ def main():
                 "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API (autograd Function); L2 flushed between reps by a 1 GiB memset the launches queue behind"}
         del x, dy, flush
 
+    # ---- decode step (inference API): 256 sequences x 32 heads, d=e=128; the fp32 states (537 MB) exceed L2 -----
+    decode = None
+    if rank == 0:
+        try:
+            bd = 256
+            st = torch.zeros((bd, H, D, D), device=dev, dtype=torch.float32)
+            qd, kd, vd = (torch.randn((bd, H, D), device=dev, generator=g).to(torch.bfloat16) for _ in range(3))
+            for _ in range(3):
+                la.lightning_attn_decode(qd, kd, vd, s, st)
+            d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            d0.record()
+            for _ in range(20):
+                la.lightning_attn_decode(qd, kd, vd, s, st)
+            d1.record()
+            torch.cuda.synchronize()
+            dms = d0.elapsed_time(d1) / 20
+            decode = {"shape": [bd, H, D, D], "ms_per_step": dms, "gbs": 8.0 * st.numel() / dms / 1e6,
+                      "tokens_per_s": bd / (dms * 1e-3), "note": "one token per sequence; bytes = fp32 state read + written"}
+            del st, qd, kd, vd
+        except Exception as ex:
+            decode = {"error": repr(ex)[:200]}
+
     # ---- long-context leg: b=1, h=32, d=e=128, 131072 tokens per GPU (the sequence-parallel shard size) ----
     # N = 1: plain single-GPU op at n = 131072. N > 1: sequence-parallel over N*131072 tokens (two NCCL
     # all-gathers of 2 MiB states per step). Same per-GPU work in both, so the ratio of the two times is the
@@ -537,7 +560,7 @@ def main():
             "config": {"workload": f"lightning2 fwd+bwd b{B} h{H} n{N_TOK} d{D} e{D} per GPU, decay slopes",
                        "l2": "inputs (4 x 1.07 GB) exceed L2; no flush needed", "parallelism": f"bh-shard x{world}, no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "srmsnorm": srms, "long_context": sp,
+            "srmsnorm": srms, "long_context": sp, "decode": decode,
         }
         emit(json.dumps(out))
     if world > 1:

@@ -80,8 +80,9 @@ size_t lab200_la_workspace_bytes(int bh, int n, int dk, int dv, int chunks);
  *   reverse = 1:  out_t = sum_{j>=t} lambda^(j-t) (a_t . bm_j) c_j
  * a, bm: (bh, n, dk); c, out: (bh, n, dv); lambda = exp(-slopes[bh % h]).
  * state_in / state_out: optional (bh, dv, dk) fp32 running state entering / leaving the sequence
- * (the transposed d x e "KV" matrix of lightning_attn2.py:55,84), for sequence-parallel chaining;
- * chaining requires n to be a multiple of 128.
+ * (the transposed d x e "KV" matrix of lightning_attn2.py:55,84), for sequence-parallel chaining and prefill/decode.
+ * Forward time: state_out is the state entering token n for any n (a ragged last block is decayed to token n, not to
+ * the end of its 128-token tile). Reverse time: chaining requires n to be a multiple of 128.
  * state_only != 0 computes only state_out (a, out may be NULL).
  * chunks: 0 = automatic, otherwise the number of sequence chunks processed by independent CTAs.
  * Stands in for _fwd_kernel (lightning_attn2.py:8-85), _bwd_intra_kernel (:88-183) and
@@ -130,6 +131,16 @@ int lab200_la_generic_resume_swapped(const void* a, const void* bm, const void* 
 int lab200_la_combine_states(const float* gathered, const float* slopes, float* out, float* out_t, int ranks,
                              int rank, int bh, int h, int x, int y, long long shard_tokens, int reverse,
                              void* stream);
+
+/*
+ * One decode step of the recurrence for every (batch, head) pair, for inference after a prefill with
+ * lab200_la_generic(..., state_out):   o = q (S + k^T v),   S <- lambda (S + k^T v).
+ * q, k: (bh, dk); v, o: (bh, dv), 16-bit; state: (bh, dv, dk) fp32, updated in place - the state entering the token,
+ * i.e. sum_{j<t} lambda^(t-j) k_j^T v_j transposed, exactly what state_out of a forward-time call holds.
+ * dk a multiple of 16. One launch, no workspace. No counterpart in the reference (it has no inference path).
+ */
+int lab200_la_decode_step(const void* q, const void* k, const void* v, const float* slopes, float* state, void* o,
+                          int bh, int h, int dk, int dv, int dtype, void* stream);
 
 /* o = LightningAttention2.forward(q, k, v, s): lightning_attn2.py:400-434 (with slopes) and
  * lightning_attn2_no_decay.py:368-400 (slopes = NULL). */

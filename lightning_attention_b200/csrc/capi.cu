@@ -308,7 +308,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   const long long total = static_cast<long long>(bh) * elems;
   const int threads = 256;
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
-  la_scan_kernel<<<blocks, threads, 0, st>>>(states, state_in, state_out, slopes, h, nchunks, elems, nblocks, bpc,
+  la_scan_kernel<<<blocks, threads, 0, st>>>(states, state_in, state_out, slopes, h, nchunks, elems, nblocks, bpc, n,
                                              p.reverse, skip_last, total);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
@@ -586,6 +586,24 @@ int lab200_la_combine_states(const float* gathered, const float* slopes, float* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   la_combine_kernel<<<dim3((y + 31) / 32, (x + 31) / 32, bh), dim3(32, 8), 0, st>>>(
       gathered, slopes, out, out_t, ranks, rank, bh, h, x, y, static_cast<float>(shard_tokens), reverse ? 1 : 0);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
+}
+
+int lab200_la_decode_step(const void* q, const void* k, const void* v, const float* slopes, float* state, void* o,
+                          int bh, int h, int dk, int dv, int dtype, void* stream) {
+  if (!q || !k || !v || !state || !o || bh < 1 || bh > 65535 || h < 1 || dk < 16 || dv < 1 || (dk % 16) != 0)
+    return LAB200_ERR_SHAPE;
+  if (dtype != LAB200_BF16 && dtype != LAB200_F16) return LAB200_ERR_DTYPE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(state)) return LAB200_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid((dv + 8 * LA_DECODE_ROWS - 1) / (8 * LA_DECODE_ROWS), bh);
+  auto qq = static_cast<const uint16_t*>(q);
+  auto kk = static_cast<const uint16_t*>(k);
+  auto vv = static_cast<const uint16_t*>(v);
+  auto oo = static_cast<uint16_t*>(o);
+  if (dtype == LAB200_BF16) la_decode_kernel<1><<<grid, 256, 0, st>>>(qq, kk, vv, slopes, state, oo, h, dk, dv);
+  else la_decode_kernel<0><<<grid, 256, 0, st>>>(qq, kk, vv, slopes, state, oo, h, dk, dv);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
 }

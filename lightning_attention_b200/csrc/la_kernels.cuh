@@ -179,6 +179,12 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const float w_out = reverse ? w_bwd : w_fwd;
   const float w_state = reverse ? w_fwd : w_bwd;
   const float decay_blk = ex2f(s2 * static_cast<float>(LA_BLOCK));
+  // A forward-time sweep that ends in a ragged block (n not a multiple of 128): the state leaving that block is decayed
+  // to token n, not to the end of the 128-token tile, so that state_out chains exactly (rows >= tail are zero padding).
+  const int tail = p.n - (p.nblocks - 1) * LA_BLOCK;
+  const bool tail_fix = !reverse && tail < LA_BLOCK && blk_end == p.nblocks;
+  const float w_tail = (tail_fix && r < tail) ? ex2f(s2 * static_cast<float>(tail - r)) : 0.f;
+  const float decay_tail = ex2f(s2 * static_cast<float>(tail));
   if (MODE == 0 && tid < LA_BLOCK) decay_tab[tid] = ex2f(s2 * static_cast<float>(tid));
 
   auto issue_A = [&](int blk) {
@@ -359,6 +365,8 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 
     // Bm rows *= w_state(r), in place (the S MMA no longer needs the unscaled tile)
+    const bool tail_blk = tail_fix && it == nb - 1;
+    const float w_st = tail_blk ? w_tail : w_state;
 #pragma unroll
     for (int i = 0; i < NKS * 4; ++i) {
       const int g = hf * NKS * 4 + i;
@@ -368,10 +376,10 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t u0, u1, u2, u3;
       ld_shared_v4(addr, u0, u1, u2, u3);
       float2 f;
-      f = unpack2<FMT>(u0); u0 = pack2<FMT>(f.x * w_state, f.y * w_state);
-      f = unpack2<FMT>(u1); u1 = pack2<FMT>(f.x * w_state, f.y * w_state);
-      f = unpack2<FMT>(u2); u2 = pack2<FMT>(f.x * w_state, f.y * w_state);
-      f = unpack2<FMT>(u3); u3 = pack2<FMT>(f.x * w_state, f.y * w_state);
+      f = unpack2<FMT>(u0); u0 = pack2<FMT>(f.x * w_st, f.y * w_st);
+      f = unpack2<FMT>(u1); u1 = pack2<FMT>(f.x * w_st, f.y * w_st);
+      f = unpack2<FMT>(u2); u2 = pack2<FMT>(f.x * w_st, f.y * w_st);
+      f = unpack2<FMT>(u3); u3 = pack2<FMT>(f.x * w_st, f.y * w_st);
       st_shared_v4(addr, u0, u1, u2, u3);
     }
     fence_proxy_async_smem();
@@ -446,7 +454,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tmem_ld32(tmem + lanebase + T_D + hf * SC + cc, dl);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) st[cc + i] = fmaf(decay_blk, st[cc + i], __uint_as_float(dl[i]));
+        for (int i = 0; i < 32; ++i) st[cc + i] = fmaf(tail_blk ? decay_tail : decay_blk, st[cc + i], __uint_as_float(dl[i]));
       }
       if (MODE == 0 && has_next) store_state_smem();
     }
@@ -481,7 +489,7 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // When `skip_last` is set the local state of the last chunk in scan order was not computed and is ignored.
 __global__ void la_scan_kernel(float* __restrict__ states, const float* __restrict__ init, float* __restrict__ total,
                                const float* __restrict__ slopes, int h, int nchunks, int elems, int nblocks,
-                               int blocks_per_chunk, int reverse, int skip_last, long long total_elems) {
+                               int blocks_per_chunk, int n, int reverse, int skip_last, long long total_elems) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total_elems) return;
   const int bh = static_cast<int>(idx / elems);
@@ -494,7 +502,9 @@ __global__ void la_scan_kernel(float* __restrict__ states, const float* __restri
     float* ptr = states + (static_cast<size_t>(bh) * nchunks + c) * elems + e;
     const float loc = (skip_last && k == nchunks - 1) ? 0.f : *ptr;
     *ptr = run;
-    run = __expf(-s * static_cast<float>(nb * LA_BLOCK)) * run + loc;
+    // forward time: the last chunk may end in a ragged block, and its local state is decayed to token n (see the block kernels)
+    const int tokens = reverse ? nb * LA_BLOCK : min(n, (c * blocks_per_chunk + nb) * LA_BLOCK) - c * blocks_per_chunk * LA_BLOCK;
+    run = __expf(-s * static_cast<float>(tokens)) * run + loc;
   }
   if (total) total[idx] = run;
 }
@@ -586,6 +596,78 @@ __global__ void la_transpose_square_kernel(float* __restrict__ m, int D) {
     const int bi = tj * 32 + r, bj = ti * 32 + tx;
     if (ai < D && aj < D) base[static_cast<size_t>(ai) * D + aj] = tb[tx][r];
     if (ti != tj && bi < D && bj < D) base[static_cast<size_t>(bi) * D + bj] = ta[tx][r];
+  }
+}
+
+// One decode step of the recurrence for every (batch, head) pair (inference; no counterpart in the reference):
+//   o = q (S + k^T v),   S <- lambda (S + k^T v),
+// S being the (dv, dk) fp32 state entering the token (what the block kernels hand out as state_out). A warp owns
+// LA_DECODE_ROWS state rows and keeps one 16-byte load per row in flight; 8 warps per CTA: grid
+// (ceil(dv / (8 LA_DECODE_ROWS)), bh), block 256. HBM-bound on the state: 8 bytes per element.
+constexpr int LA_DECODE_ROWS = 8;
+
+template <int FMT>
+__global__ void __launch_bounds__(256)
+la_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
+                 const float* __restrict__ slopes, float* __restrict__ state, uint16_t* __restrict__ o, int h, int dk,
+                 int dv) {
+  const int bh = blockIdx.y;
+  const int row0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * LA_DECODE_ROWS;
+  const int lane = threadIdx.x & 31;
+  if (row0 >= dv) return;
+  const float lam = slopes ? __expf(-slopes[bh % h]) : 1.f;
+  auto to_f = [](uint32_t x) -> float {  // low 16 bits of x
+    if constexpr (FMT == 1) return __uint_as_float(x << 16);
+    else return __half2float(__ushort_as_half(static_cast<unsigned short>(x & 0xffffu)));
+  };
+  float ve[LA_DECODE_ROWS], acc[LA_DECODE_ROWS];
+#pragma unroll
+  for (int j = 0; j < LA_DECODE_ROWS; ++j) {
+    ve[j] = (row0 + j < dv) ? to_f(v[static_cast<size_t>(bh) * dv + row0 + j]) : 0.f;
+    acc[j] = 0.f;
+  }
+  const uint16_t* qp = q + static_cast<size_t>(bh) * dk;
+  const uint16_t* kp = k + static_cast<size_t>(bh) * dk;
+  float* sp = state + (static_cast<size_t>(bh) * dv + row0) * dk;
+  for (int c = lane * 4; c < dk; c += 128) {
+    float4 st[LA_DECODE_ROWS];
+#pragma unroll
+    for (int j = 0; j < LA_DECODE_ROWS; ++j)
+      st[j] = (row0 + j < dv) ? *reinterpret_cast<const float4*>(sp + static_cast<size_t>(j) * dk + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint2 qq = *reinterpret_cast<const uint2*>(qp + c);
+    const uint2 kk = *reinterpret_cast<const uint2*>(kp + c);
+    const float k0 = to_f(kk.x & 0xffffu), k1 = to_f(kk.x >> 16), k2 = to_f(kk.y & 0xffffu), k3 = to_f(kk.y >> 16);
+    const float q0 = to_f(qq.x & 0xffffu), q1 = to_f(qq.x >> 16), q2 = to_f(qq.y & 0xffffu), q3 = to_f(qq.y >> 16);
+#pragma unroll
+    for (int j = 0; j < LA_DECODE_ROWS; ++j) {
+      float4 nw;
+      nw.x = fmaf(k0, ve[j], st[j].x);
+      nw.y = fmaf(k1, ve[j], st[j].y);
+      nw.z = fmaf(k2, ve[j], st[j].z);
+      nw.w = fmaf(k3, ve[j], st[j].w);
+      acc[j] = fmaf(q0, nw.x, fmaf(q1, nw.y, fmaf(q2, nw.z, fmaf(q3, nw.w, acc[j]))));
+      if (row0 + j < dv)
+        *reinterpret_cast<float4*>(sp + static_cast<size_t>(j) * dk + c) = make_float4(lam * nw.x, lam * nw.y, lam * nw.z, lam * nw.w);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < LA_DECODE_ROWS; ++j) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+  }
+  if (lane < LA_DECODE_ROWS && row0 + lane < dv) {
+    float mine = acc[0];
+#pragma unroll
+    for (int j = 1; j < LA_DECODE_ROWS; ++j) mine = (lane == j) ? acc[j] : mine;
+    uint16_t out;
+    if constexpr (FMT == 1) {
+      const __nv_bfloat16 bb = __float2bfloat16_rn(mine);
+      out = *reinterpret_cast<const uint16_t*>(&bb);
+    } else {
+      const __half hh = __float2half_rn(mine);
+      out = *reinterpret_cast<const uint16_t*>(&hh);
+    }
+    o[static_cast<size_t>(bh) * dv + row0 + lane] = out;
   }
 }
 

@@ -348,6 +348,13 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const float decay_blk = ex2f(s2 * static_cast<float>(LA_BLOCK));
     const float w_state = reverse ? ex2f(s2 * static_cast<float>(r)) : ex2f(s2 * static_cast<float>(LA_BLOCK - r));
     const uint32_t w_state2 = pack2<FMT>(w_state, w_state);
+    // A forward-time sweep that ends in a ragged block (n not a multiple of 128): the state leaving that block is decayed
+    // to token n, not to the end of the 128-token tile, so that state_out chains exactly (rows >= tail are zero padding).
+    const int tail = p.n - (p.nblocks - 1) * LA_BLOCK;
+    const bool tail_fix = !reverse && tail < LA_BLOCK && blk_end == p.nblocks;
+    const float w_tail = (tail_fix && r < tail) ? ex2f(s2 * static_cast<float>(tail - r)) : 0.f;
+    const uint32_t w_tail2 = pack2<FMT>(w_tail, w_tail);
+    const float decay_tail = ex2f(s2 * static_cast<float>(tail));
     const bool st_row_valid = (r < DV) && (dv_off + r < p.dv);
     const bool store_thread = (w8 == 0 && lane == 0);
 
@@ -392,6 +399,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) return false;
       if (s != 0.f) {
+        const uint32_t w2 = (tail_fix && j == nb - 1) ? w_tail2 : w_state2;
         constexpr int NCH = NKS * 4;  // chunks per thread
         const uint32_t sBs = sB + st * NKS * SLAB;
         uint32_t u[NCH][4];
@@ -407,7 +415,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
 #pragma unroll
-          for (int j2 = 0; j2 < 4; ++j2) u[c][j2] = mul2<FMT>(u[c][j2], w_state2);
+          for (int j2 = 0; j2 < 4; ++j2) u[c][j2] = mul2<FMT>(u[c][j2], w2);
           st_shared_v4(addr[c], u[c][0], u[c][1], u[c][2], u[c][3]);
         }
         fence_proxy_async_smem();
@@ -444,7 +452,8 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tmem_ld32(tmem + lanebase + T_D + hf * SC + cc, dl);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) stt[cc + i] = fmaf(decay_blk, stt[cc + i], __uint_as_float(dl[i]));
+          for (int i = 0; i < 32; ++i)
+            stt[cc + i] = fmaf((tail_fix && it == nb - 1) ? decay_tail : decay_blk, stt[cc + i], __uint_as_float(dl[i]));
         }
       }
       tc_fence_before_sync();

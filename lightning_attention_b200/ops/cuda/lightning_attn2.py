@@ -236,6 +236,48 @@ class LightningAttention2NoDecay(torch.autograd.Function):
         return dq, dk, dv
 
 
+def lightning_attn_prefill(q, k, v, s=None, kv_state=None):
+    """Forward pass that carries the recurrence state, for inference (no autograd; the reference has no such entry).
+
+    q, k: (b, h, n, d); v: (b, h, n, e); d, e multiples of 16, d <= 256; any n. kv_state: None or the (b, h, e, d) fp32
+    state entering the first token, i.e. what an earlier call returned. Returns (o, kv_state_out) where kv_state_out
+    is the state entering token n: sum_{j<n} lambda^(n-j) k_j^T v_j (transposed) plus the decayed incoming state.
+    Feeding it to the next prefill chunk or to `lightning_attn_decode` continues the sequence exactly."""
+    _check_inputs(q, k, v)
+    with torch.no_grad():
+        o, st = la_generic(q.detach(), k.detach(), v.detach(), None if s is None else s.detach(), state_in=kv_state,
+                           want_state=True)
+    return o, st
+
+
+def lightning_attn_decode(q, k, v, s, kv_state):
+    """One token per (batch, head): o = q (S + k^T v), S <- lambda (S + k^T v), S = kv_state updated IN PLACE.
+
+    q, k: (b, h, d) or (b, h, 1, d); v: (b, h, e) or (b, h, 1, e); kv_state: (b, h, e, d) fp32 contiguous, from
+    `lightning_attn_prefill` (or zeros for an empty prefix). Returns o shaped like v. No autograd."""
+    _lib.require_cuda(q, k, v, kv_state)
+    squeeze = q.dim() == 4
+    if squeeze:
+        if q.shape[2] != 1 or k.shape[2] != 1 or v.shape[2] != 1:
+            raise RuntimeError("lightning_attn_decode takes exactly one token per call")
+        q, k, v = q[:, :, 0], k[:, :, 0], v[:, :, 0]
+    b, h, d = q.shape
+    e = v.shape[-1]
+    if k.shape != q.shape or v.shape[:2] != q.shape[:2] or not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError(f"expected q, k (b, h, d) and v (b, h, e) of one dtype; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if tuple(kv_state.shape) != (b, h, e, d) or kv_state.dtype != torch.float32 or not kv_state.is_contiguous():
+        raise RuntimeError(f"kv_state must be a contiguous fp32 tensor of shape {(b, h, e, d)}")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    sl = _slopes_arg(s, h, q.device)
+    o = torch.empty((b, h, e), dtype=q.dtype, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().lab200_la_decode_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), kv_state.data_ptr(),
+                                              o.data_ptr(), b * h, h, d, e, _lib.dtype_code(q.dtype),
+                                              _lib.stream_ptr(q.device))
+    _lib.check(rc, "lab200_la_decode_step")
+    return o.unsqueeze(2) if squeeze else o
+
+
 lightning_attn2 = LightningAttention2.apply
 lightning_attn2_no_decay = LightningAttention2NoDecay.apply
 # The reference's "parallel" variant (lightning_attn2_parallel.py:1072) computes the same function with a

@@ -418,3 +418,60 @@ def test_autograd_in_chunk_mode_hands_chunk_states_from_forward_to_backward(cuda
     compare_with_torch_reference(q, k, v, do, s, (o.detach(),) + first, False, f"autograd-chunked-decay{decay}")
     for x, y in zip(first, second):
         assert_parity(x, y.float(), "second-backward", False)
+
+
+@pytest.mark.parametrize("n,dk,dv,chunks", [(300, 64, 64, 1), (171, 128, 128, 1), (1000, 128, 64, 3), (77, 192, 192, 1), (129, 32, 48, 2)])
+@pytest.mark.parametrize("slope_scale", [1.0, 0.05, 0.0])
+def test_forward_state_out_is_exact_for_ragged_lengths(cuda_lib, n, dk, dv, chunks, slope_scale):
+    """state_out of a forward-time call is the state entering token n for any n: checked against the definition
+    (oracle.state_entering), with and without an incoming state, in one sweep and in chunk mode."""
+    torch.manual_seed(21)
+    b, h = 1, 3
+    a, bm = (torch.randn((b, h, n, dk), device=DEV).bfloat16() for _ in range(2))
+    c = torch.randn((b, h, n, dv), device=DEV).bfloat16()
+    s = (la._build_slope_tensor(h).reshape(-1) * slope_scale).to(DEV) if slope_scale > 0 else None
+    f = lambda t: None if t is None else t.float().cpu().numpy()
+    for st_in in (None, torch.randn((b, h, dv, dk), device=DEV)):
+        _, st = c_generic(cuda_lib, a, bm, c, s, False, st_in, True, chunks)
+        ref = O.state_entering(f(bm), f(c), f(s), state_in=f(st_in))
+        assert O.rel_l2_err(f(st), ref) <= 1e-2, (n, dk, dv, chunks, st_in is not None)
+        st_only = c_generic(cuda_lib, None, bm, c, s, False, st_in, True, chunks, state_only=True)[1]
+        assert O.rel_l2_err(f(st_only), ref) <= 1e-2
+
+
+@pytest.mark.parametrize("d,e", [(128, 128), (64, 96), (192, 192)])
+@pytest.mark.parametrize("decay", [True, False])
+def test_prefill_chunks_and_decode_steps_continue_the_sequence(cuda_lib, d, e, decay):
+    """prefill(0..n1) -> prefill(n1..n2, state) -> decode steps == one forward over the whole sequence."""
+    torch.manual_seed(22)
+    b, h, n, n1, n2 = 2, 4, 700, 300, 684
+    q, k = (torch.randn((b, h, n, d), device=DEV).bfloat16() for _ in range(2))
+    v = torch.randn((b, h, n, e), device=DEV).bfloat16()
+    s = (la._build_slope_tensor(h) * 0.2).to(DEV) if decay else None
+    ref = torch_la_reference(q, k, v, s)
+    o1, st = la.lightning_attn_prefill(q[:, :, :n1].contiguous(), k[:, :, :n1].contiguous(), v[:, :, :n1].contiguous(), s)
+    o2, st = la.lightning_attn_prefill(q[:, :, n1:n2].contiguous(), k[:, :, n1:n2].contiguous(), v[:, :, n1:n2].contiguous(), s, st)
+    outs = [o1, o2]
+    for t in range(n2, n):
+        outs.append(la.lightning_attn_decode(q[:, :, t:t + 1], k[:, :, t:t + 1], v[:, :, t:t + 1], s, st))
+    got = torch.cat(outs, dim=2)
+    assert_parity(got, ref, f"prefill+decode d{d} e{e}", False)
+    assert_parity(got[:, :, n2:], ref[:, :, n2:], "decode steps", False)
+    f = lambda t: None if t is None else t.float().cpu().numpy()
+    assert O.rel_l2_err(f(st), O.state_entering(f(k), f(v), f(s))) <= 1e-2
+
+
+def test_decode_step_against_numpy_oracle(cuda_lib):
+    torch.manual_seed(23)
+    b, h, d, e = 3, 5, 48, 80
+    q, k = (torch.randn((b, h, d), device=DEV).half() for _ in range(2))
+    v = torch.randn((b, h, e), device=DEV).half()
+    st = torch.randn((b, h, e, d), device=DEV)
+    s = la._build_slope_tensor(h).to(DEV)
+    f = lambda t: t.float().cpu().numpy()
+    ro, rst = O.decode_step(f(q), f(k), f(v), f(s), f(st))
+    o = la.lightning_attn_decode(q, k, v, s, st)
+    assert O.rel_l2_err(f(o), ro) <= 2e-3
+    assert O.rel_l2_err(f(st), rst) <= 1e-6
+    with pytest.raises(RuntimeError):
+        la.lightning_attn_decode(q, k, v, s, st.transpose(2, 3))

@@ -131,3 +131,23 @@ def test_sequence_parallel_chain_equals_single(reverse, scale):
     outs = [O.la_generic(a[:, :, x], bm[:, :, x], c[:, :, x], s, reverse=reverse, state_in=incoming[r])[0]
             for r, x in enumerate(sl)]
     assert O.max_abs_err(np.concatenate(outs, axis=2), full) < 1e-9
+
+
+def test_state_and_decode_chain_matches_definition():
+    """The exported state (entering token n, ragged n included) and the decode step, against the O(n^2) definition."""
+    rng = np.random.default_rng(5)
+    b, h, n, d, e = 1, 3, 300, 16, 24
+    q, k = rng.standard_normal((2, b, h, n, d))
+    v = rng.standard_normal((b, h, n, e))
+    s = O.build_slopes(h) * 0.3
+    ref = O.linear_attn(q, k, v, s)
+    n1, n2 = 171, 290
+    o1, st = O.la_generic(q[:, :, :n1], k[:, :, :n1], v[:, :, :n1], s)
+    assert O.max_abs_err(st, O.state_entering(k[:, :, :n1], v[:, :, :n1], s)) < 1e-10
+    o2, st = O.la_generic(q[:, :, n1:n2], k[:, :, n1:n2], v[:, :, n1:n2], s, state_in=st)
+    assert O.max_abs_err(st, O.state_entering(k[:, :, :n2], v[:, :, :n2], s)) < 1e-10
+    outs = [o1, o2]
+    for t in range(n2, n):
+        o, st = O.decode_step(q[:, :, t], k[:, :, t], v[:, :, t], s, st)
+        outs.append(o[:, :, None])
+    assert O.max_abs_err(np.concatenate(outs, axis=2), ref) < 1e-10
