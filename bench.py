@@ -185,19 +185,35 @@ def run_sweep(emit):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    flush_box = [flush]
 
     def timed(fn, reps=15, warm=5):
+        if flush_box[0] is None:
+            flush_box[0] = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
         for _ in range(warm):
             fn()
         ts = []
         for _ in range(reps):
-            flush.zero_()
+            flush_box[0].zero_()
             a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); fn(); b_.record()
             torch.cuda.synchronize()
             ts.append(a.elapsed_time(b_))
         return statistics.median(ts)
 
+    def peak_mb(fn):
+        """Peak allocated memory of one call, inputs included, as the reference's memory table measures it
+        (benchmarks/benchmark_lightning2.py:160-190: reset the peak, run, read torch.cuda.max_memory_allocated)."""
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats(dev)
+        fn()
+        torch.cuda.synchronize()
+        return torch.cuda.max_memory_allocated(dev) / 1024 / 1024
+
+    def drop_flush():  # the memory columns should not carry the flush buffer
+        flush_box[0] = None
+
+    del flush
     torch.manual_seed(SEED)
     s = la._build_slope_tensor(H).to(dev)
     for n in (512, 1024, 2048, 4096, 8192, 16384, 32768):
@@ -213,8 +229,20 @@ def run_sweep(emit):
                 o.backward(do, retain_graph=True)
 
             bwd = timed(bwd_fn)
+            drop_flush()
+            del o
+            q.grad = k.grad = v.grad = None
+            fwd_mb = peak_mb(lambda: fn())
+
+            def fwd_bwd():
+                fn().backward(do)
+
+            bwd_mb = peak_mb(fwd_bwd)
+            q.grad = k.grad = v.grad = None
             units = B * H * n
             emit(json.dumps({"table": name, "n": n, "fwd_ms": fwd, "bwd_ms": bwd, "ref_fwd_ms": ref_f[n], "ref_bwd_ms": ref_b[n],
+                              "fwd_peak_mb": fwd_mb, "fwd_bwd_peak_mb": bwd_mb,
+                              "ref_fwd_peak_mb": 64.0 * n / 512, "ref_bwd_peak_mb": 173.6 * n / 512,
                               "tokens_per_s_fwd_bwd": B * n / ((fwd + bwd) * 1e-3),
                               "hbm_frac_of_measured": ALG_BYTES_PER_UNIT * units / ((fwd + bwd) * 1e-3) / 1e9 / load_peaks()[0]}))
         del q, k, v, do
@@ -411,6 +439,44 @@ def main():
                 "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API (autograd Function); L2 flushed between reps by a 1 GiB memset the launches queue behind"}
         del x, dy, flush
 
+    # ---- projection layout: q, k, v, do as (b, h, n, d) views of (b, n, h, d) tensors, as a caller's projections give them.
+    # "in_place": the op reads and writes that layout directly. "with_copies": what the reference's wrapper does with such
+    # views - .contiguous() on q, k, v and do, and a rearranging copy of o and of the three gradients on the way back.
+    proj = None
+    if rank == 0:
+        try:
+            xq, xk, xv = (t.detach().transpose(1, 2).contiguous().requires_grad_() for t in (q, k, v))
+            xdo = do.transpose(1, 2).contiguous()
+
+            def in_place():
+                xq.grad = xk.grad = xv.grad = None
+                o_ = la.lightning_attn2(xq.transpose(1, 2), xk.transpose(1, 2), xv.transpose(1, 2), s)
+                o_.backward(xdo.transpose(1, 2))
+
+            def with_copies():
+                xq.grad = xk.grad = xv.grad = None
+                o_ = la.lightning_attn2(xq.transpose(1, 2).contiguous(), xk.transpose(1, 2).contiguous(),
+                                        xv.transpose(1, 2).contiguous(), s)
+                o_.transpose(1, 2).contiguous().backward(xdo)
+
+            res = {}
+            for name, fn in (("in_place", in_place), ("with_copies", with_copies)):
+                for _ in range(2):
+                    fn()
+                p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                p0.record()
+                for _ in range(5):
+                    fn()
+                p1.record()
+                torch.cuda.synchronize()
+                res[name + "_ms"] = p0.elapsed_time(p1) / 5
+            proj = {"shape_b_n_h_d": [B, N_TOK, H, D], **res,
+                    "note": "fwd+bwd with q, k, v, do given as (b, n, h, d) tensors; tnl_attn.py:56-64 style caller"}
+            del xq, xk, xv, xdo
+        except Exception as ex:
+            proj = {"error": repr(ex)[:200]}
+
     # ---- decode step (inference API): 256 sequences x 32 heads, d=e=128; the fp32 states (537 MB) exceed L2 -----
     decode = None
     if rank == 0:
@@ -560,7 +626,7 @@ def main():
             "config": {"workload": f"lightning2 fwd+bwd b{B} h{H} n{N_TOK} d{D} e{D} per GPU, decay slopes",
                        "l2": "inputs (4 x 1.07 GB) exceed L2; no flush needed", "parallelism": f"bh-shard x{world}, no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "srmsnorm": srms, "long_context": sp, "decode": decode,
+            "srmsnorm": srms, "long_context": sp, "decode": decode, "projection_layout": proj,
         }
         emit(json.dumps(out))
     if world > 1:

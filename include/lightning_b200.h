@@ -30,6 +30,11 @@ extern "C" {
 #define LAB200_F32 0
 #define LAB200_F16 1
 #define LAB200_BF16 2
+/* Layout flag, OR-ed into the dtype argument of the attention entry points (lab200_la_generic*, lab200_la2_fwd*,
+ * lab200_la2_bwd): every 16-bit tensor of the call is (b, n, h, dim) contiguous - what the projection GEMMs around the
+ * op produce and consume (examples/module/tnl_attn.py:56-64 rearranges to (b, h, n, d) and back) - instead of
+ * (b, h, n, dim). States stay (bh, dv, dk). Needs bh = b * h with whole batches and dk <= 128. */
+#define LAB200_LAYOUT_BNHD 0x100
 
 #define LAB200_OK 0
 #define LAB200_ERR_SHAPE 1       /* unsupported or inconsistent sizes */

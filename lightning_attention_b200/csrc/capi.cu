@@ -53,11 +53,19 @@ int sm_count() {
 
 // (bh, n, dim) row-major 16-bit tensor -> boxes of 64 features x 128 tokens, 128-byte swizzle,
 // out-of-range rows and columns read as zero.
-int make_tmap(CUtensorMap* tm, const void* ptr, int bh, int n, int dim, int dtype) {
+// layout 1: the tensor is (b, n, h, dim) contiguous instead. Token t of pair (b, hd) then starts at element
+// ((b n + t) h + hd) dim = (b n h + hd) dim + t (h dim): still a three-dimensional map, with token stride h dim and a
+// third dimension of extent b n h and stride dim that the kernel indexes by b n h + hd; tokens >= n stay out of range.
+int make_tmap(CUtensorMap* tm, const void* ptr, int bh, int n, int dim, int dtype, int layout = 0, int h = 1) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return LAB200_ERR_DRIVER;
-  const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(dim), static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(bh)};
-  const cuuint64_t gstr[2] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(n) * dim * 2};
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(dim), static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(bh)};
+  cuuint64_t gstr[2] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(n) * dim * 2};
+  if (layout) {
+    gdim[2] = static_cast<cuuint64_t>(bh) * n;  // b n h
+    gstr[0] = static_cast<cuuint64_t>(h) * dim * 2;
+    gstr[1] = static_cast<cuuint64_t>(dim) * 2;
+  }
   const cuuint32_t box[3] = {64, LA_BLOCK, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = (dtype == LAB200_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -228,6 +236,8 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
                     int resume = 0) {
   int rc = la_validate(a, bm, c, out, state_in, state_out, workspace, bh, h, n, dk, dv, state_only, dtype);
   if (rc != LAB200_OK) return rc;
+  const int layout = (dtype & LAB200_LAYOUT_BNHD) ? 1 : 0;
+  dtype &= 0xff;
   Tiling t;
   pick_tiling(dk, dv, &t);
   const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
@@ -238,14 +248,14 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   if (!workspace || workspace_bytes < need) return LAB200_ERR_WORKSPACE;
 
   CUtensorMap tA, tB, tC, tO;
-  if ((rc = make_tmap(&tB, bm, bh, n, dk, dtype)) != LAB200_OK) return rc;
-  if ((rc = make_tmap(&tC, c, bh, n, dv, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tB, bm, bh, n, dk, dtype, layout, h)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tC, c, bh, n, dv, dtype, layout, h)) != LAB200_OK) return rc;
   if (state_only) {
     tA = tB;
     tO = tC;
   } else {
-    if ((rc = make_tmap(&tA, a, bh, n, dk, dtype)) != LAB200_OK) return rc;
-    if ((rc = make_tmap(&tO, out, bh, n, dv, dtype)) != LAB200_OK) return rc;  // output tiles leave through TMA stores
+    if ((rc = make_tmap(&tA, a, bh, n, dk, dtype, layout, h)) != LAB200_OK) return rc;
+    if ((rc = make_tmap(&tO, out, bh, n, dv, dtype, layout, h)) != LAB200_OK) return rc;  // output tiles leave through TMA stores
   }
 
   LaParams p;
@@ -256,6 +266,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   p.nblocks = nblocks;
   p.blocks_per_chunk = bpc;
   p.reverse = reverse ? 1 : 0;
+  p.layout = layout;
   p.nstage = 2;
   p.wait_budget = WAIT_BUDGET;
   p.trace = g_trace.load(std::memory_order_relaxed);
@@ -393,9 +404,15 @@ int la_dkdv_impl(const void* q, const void* k, const void* v, const void* dout, 
 int la_validate(const void* a, const void* bm, const void* c, const void* out, const float* state_in,
                 const float* state_out, const void* workspace, int bh, int h, int n, int dk, int dv, int state_only,
                 int dtype) {
+  const int layout = dtype & LAB200_LAYOUT_BNHD;
+  dtype &= 0xff;
   if (dtype != LAB200_BF16 && dtype != LAB200_F16) return LAB200_ERR_DTYPE;
   Tiling t;
   if (bh < 1 || bh > 65535 || h < 1 || n < 1 || !pick_tiling(dk, dv, &t)) return LAB200_ERR_SHAPE;
+  // (b, n, h, dim) tensors: whole batches of h heads, third tensor-map coordinate b n h + head within int range, and
+  // only the pipelined kernel (dk <= 128) reads and writes them
+  if (layout && ((bh % h) != 0 || static_cast<long long>(bh) * n >= (1LL << 31) || t.nks > 2 || !use_pipelined_kernel()))
+    return LAB200_ERR_SHAPE;
   if (!bm || !c || (!state_only && (!a || !out)) || (state_only && !state_out)) return LAB200_ERR_SHAPE;
   if (!aligned16(a) || !aligned16(bm) || !aligned16(c) || !aligned16(out) || !aligned16(state_in) ||
       !aligned16(state_out) || !aligned16(workspace))
@@ -659,7 +676,7 @@ int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slo
     const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
     int nchunks = chunks > 0 ? chunks : plan_chunks(bh, n, e, d);
     if (nchunks > nblocks) nchunks = nblocks;
-    if (nchunks == 1 && use_fused_dkdv()) {
+    if (nchunks == 1 && use_fused_dkdv() && !(dtype & LAB200_LAYOUT_BNHD)) {
       rc = la_dkdv_impl(q, k, v, dout, slopes, dk, dv, workspace, bh, h, n, d, e, dtype, st);
       if (rc != LAB200_ERR_SHAPE) return rc;
     }

@@ -64,6 +64,8 @@ struct LaParams {
   int chunk0;              // chunk handled by blockIdx.y == 0
   int state_slots;         // chunk slots per (batch, head) in state_in / state_out
   int reverse;
+  int layout;              // 0: tensors are (b, h, n, dim) contiguous; 1: (b, n, h, dim) contiguous (pipelined kernel only):
+                           // the tensor maps then index their third dimension by batch * n * h + head, see make_tmap
   int nstage;              // 1 or 2 shared-memory stages for the Bm and C tiles
   long long wait_budget;   // clock cycles after which a barrier wait gives up
   long long* trace;        // optional: CTA (0,0,0) records clock64() stamps here, LA_TRACE_SLOTS per block

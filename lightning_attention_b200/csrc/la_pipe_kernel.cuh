@@ -104,6 +104,8 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int blk_end = min(p.nblocks, blk_begin + p.blocks_per_chunk);
   const int nb = blk_end - blk_begin;
   const int reverse = p.reverse;
+  // third tensor-map coordinate of this (batch, head) pair
+  const int zc = p.layout ? (bh / p.h) * p.n * p.h + (bh % p.h) : bh;
   const int nk16 = p.dk >> 4;
   const long long budget = p.wait_budget;
   const bool have_state_in = (p.state_in != nullptr);
@@ -151,7 +153,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!lap_wait(bar(LAP_O_STAGED, sst), (i >> 1) & 1, abort_flag, budget)) return false;
 #pragma unroll
         for (int vs = 0; vs < NVS; ++vs)
-          tma_store_3d(&tmO, sA + (sst * NAS + vs) * SLAB, dv_off + vs * 64, blk_of(i) * LA_BLOCK, bh);
+          tma_store_3d(&tmO, sA + (sst * NAS + vs) * SLAB, dv_off + vs * 64, blk_of(i) * LA_BLOCK, zc);
         tma_store_commit();
         return true;
       };
@@ -172,16 +174,16 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_arrive_expect_tx(bar(LAP_FULL_BC, st), (NKS + 2) * SLAB);
 #pragma unroll
         for (int ks = 0; ks < NKS; ++ks)
-          tma_load_3d(sB + (st * NKS + ks) * SLAB, &tmB, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_BC, st));
+          tma_load_3d(sB + (st * NKS + ks) * SLAB, &tmB, ks * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_BC, st));
 #pragma unroll
         for (int vs = 0; vs < 2; ++vs)
-          tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_BC, st));
+          tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_BC, st));
         if (MODE == 0) {
           if (it >= 2) tma_store_wait_read();
           mbar_arrive_expect_tx(bar(LAP_FULL_A, st), NKS * SLAB);
 #pragma unroll
           for (int ks = 0; ks < NKS; ++ks)
-            tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, bh, bar(LAP_FULL_A, st));
+            tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_A, st));
         }
       }
       if (MODE == 0 && alive && *abort_flag == 0) {

@@ -22,6 +22,42 @@ def _slopes_arg(s, h, device):
     return flat[:h].contiguous()
 
 
+LAYOUT_BNHD = 0x100  # LAB200_LAYOUT_BNHD
+
+
+def _is_bnhd(t):
+    """True if the (b, h, n, d) tensor is a view of a contiguous (b, n, h, d) one - what
+    `rearrange(x, "b n (h d) -> b h n d")` of a projection output gives (examples/module/tnl_attn.py:56-59)."""
+    if t is None or t.dim() != 4:
+        return False
+    b, h, n, d = t.shape
+    return h > 1 and n > 1 and t.stride() == (n * h * d, d, h * d, 1) and t.data_ptr() % 16 == 0
+
+
+def _empty_bnhd(b, h, n, d, dtype, device):
+    return torch.empty((b, n, h, d), dtype=dtype, device=device).transpose(1, 2)
+
+
+def _to_layout(t, bnhd):
+    """`t` in the layout the call uses: as is when it already has it, else one copy."""
+    if not bnhd:
+        return t.contiguous()
+    if _is_bnhd(t):
+        return t
+    b, h, n, d = t.shape
+    return _empty_bnhd(b, h, n, d, t.dtype, t.device).copy_(t)
+
+
+def _use_bnhd(*tensors):
+    """The library reads (b, n, h, dim) tensors in place when every tensor of the call has that layout and all feature
+    dims are <= 128 (the pipelined kernel); anything else is made (b, h, n, dim) contiguous first, as the reference does."""
+    return all(_is_bnhd(t) for t in tensors) and all(t.shape[-1] <= 128 and t.shape[-1] % 16 == 0 for t in tensors)
+
+
+def _empty_out(b, h, n, d, dtype, device, bnhd):
+    return _empty_bnhd(b, h, n, d, dtype, device) if bnhd else torch.empty((b, h, n, d), dtype=dtype, device=device)
+
+
 def _workspace(nbytes, device):
     return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
 
@@ -37,7 +73,7 @@ class KeptWorkspace:
 
 def _product_key(bm, c, reverse, chunks):
     b, h, n, dk = bm.shape
-    return (b, h, n, dk, c.shape[-1], bool(reverse), int(chunks), bm.dtype, bm.data_ptr(), c.data_ptr())
+    return (b, h, n, dk, c.shape[-1], bool(reverse), int(chunks), bm.dtype, bm.data_ptr(), c.data_ptr(), bm.stride(), c.stride())
 
 
 def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False, state_only=False, chunks=0,
@@ -61,13 +97,16 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
     b, h, n, dk = bm.shape
     dv = c.shape[-1]
     dev = bm.device
-    if (resume_from is not None or keep_workspace) and not (bm.is_contiguous() and c.is_contiguous()):
-        raise RuntimeError("keep_workspace / resume_from need contiguous bm and c (the handle is tied to their storage)")
-    bm = bm.contiguous()
-    c = c.contiguous()
-    a = None if state_only else a.contiguous()
+    bnhd = _use_bnhd(bm, c) if state_only else _use_bnhd(a, bm, c)
+    if (resume_from is not None or keep_workspace) and not bnhd and not (bm.is_contiguous() and c.is_contiguous()):
+        raise RuntimeError("keep_workspace / resume_from need bm and c in one of the two layouts the library reads in "
+                           "place (the handle is tied to their storage)")
+    bm = _to_layout(bm, bnhd)
+    c = _to_layout(c, bnhd)
+    a = None if state_only else _to_layout(a, bnhd)
     sl = _slopes_arg(s, h, dev)
-    out = None if state_only else torch.empty((b, h, n, dv), dtype=bm.dtype, device=dev)
+    out = None if state_only else _empty_out(b, h, n, dv, bm.dtype, dev, bnhd)
+    dt = _lib.dtype_code(bm.dtype) | (LAYOUT_BNHD if bnhd else 0)
     if state_in is not None:
         state_in = state_in.to(device=dev, dtype=torch.float32).contiguous()
         if tuple(state_in.shape) != (b, h, dv, dk):
@@ -90,11 +129,11 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
                 rc = L.lab200_la_generic_resume_swapped(
                     _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in), hd.ws.data_ptr(),
                     hd.nbytes, b * h, h, n, dk, dv, int(bool(reverse)), int(chunks), int(bool(rebase)),
-                    _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
+                    dt, _lib.stream_ptr(dev))
             else:
                 rc = L.lab200_la_generic_resume(
                     _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in), hd.ws.data_ptr(),
-                    hd.nbytes, b * h, h, n, dk, dv, int(bool(reverse)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
+                    hd.nbytes, b * h, h, n, dk, dv, int(bool(reverse)), int(chunks), dt, _lib.stream_ptr(dev))
         _lib.check(rc, "lab200_la_generic_resume")
         hd.key = _product_key(bm, c, reverse, chunks)  # a swapped resume hands the workspace over to this product
         hd.based = True
@@ -108,33 +147,35 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
         rc = L.lab200_la_generic(
             _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in),
             _lib.ptr(state_out), ws.data_ptr(), nbytes, b * h, h, n, dk, dv, int(bool(reverse)),
-            int(bool(state_only)), int(chunks), _lib.dtype_code(bm.dtype), _lib.stream_ptr(dev))
+            int(bool(state_only)), int(chunks), dt, _lib.stream_ptr(dev))
     _lib.check(rc, "lab200_la_generic")
     if keep_workspace:
         return out, state_out, KeptWorkspace(ws, nbytes, _product_key(bm, c, reverse, chunks), based=not state_only)
     return out, state_out
 
 
-def _fwd(q, k, v, sl, chunks=0):
+def _fwd(q, k, v, sl, chunks=0, bnhd=False):
+    """q, k, v all in one layout: (b, h, n, dim) contiguous, or (bnhd=True) views of (b, n, h, dim) tensors."""
     b, h, n, d = q.shape
     e = v.shape[-1]
-    o = torch.empty((b, h, n, e), dtype=q.dtype, device=q.device)
+    o = _empty_out(b, h, n, e, q.dtype, q.device, bnhd)
     L = _lib.lib()
     nbytes = L.lab200_la_workspace_bytes(b * h, n, d, e, chunks)
     ws = _workspace(nbytes, q.device)
     with torch.cuda.device(q.device):
         rc = L.lab200_la2_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), o.data_ptr(), ws.data_ptr(),
-                              nbytes, b, h, n, d, e, int(chunks), _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device))
+                              nbytes, b, h, n, d, e, int(chunks), _lib.dtype_code(q.dtype) | (LAYOUT_BNHD if bnhd else 0),
+                              _lib.stream_ptr(q.device))
     _lib.check(rc, "lab200_la2_fwd")
     return o
 
 
-def _bwd(q, k, v, sl, do, chunks=0):
+def _bwd(q, k, v, sl, do, chunks=0, bnhd=False):
     b, h, n, d = q.shape
     e = v.shape[-1]
-    dq = torch.empty_like(q)
-    dk = torch.empty_like(k)
-    dv = torch.empty_like(v)
+    dq = _empty_out(b, h, n, d, q.dtype, q.device, bnhd)
+    dk = _empty_out(b, h, n, d, q.dtype, q.device, bnhd)
+    dv = _empty_out(b, h, n, e, q.dtype, q.device, bnhd)
     L = _lib.lib()
     m = max(d, e)
     nbytes = L.lab200_la_workspace_bytes(b * h, n, m, m, chunks)
@@ -142,7 +183,7 @@ def _bwd(q, k, v, sl, do, chunks=0):
     with torch.cuda.device(q.device):
         rc = L.lab200_la2_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), do.data_ptr(), dq.data_ptr(),
                               dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), nbytes, b, h, n, d, e, int(chunks),
-                              _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device))
+                              _lib.dtype_code(q.dtype) | (LAYOUT_BNHD if bnhd else 0), _lib.stream_ptr(q.device))
     _lib.check(rc, "lab200_la2_bwd")
     return dq, dk, dv
 
@@ -184,28 +225,28 @@ class LightningAttention2(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, s):
         _check_inputs(q, k, v)
-        q = q.contiguous()
-        k = k.contiguous()
-        v = v.contiguous()
+        bnhd = _use_bnhd(q, k, v)  # read (b, n, h, dim) projections in place, write o the same way: no transposing copies
+        q, k, v = (_to_layout(t, bnhd) for t in (q, k, v))
         s = s.contiguous()
         sl = _slopes_arg(s, q.shape[1], q.device)
         ctx.kept = None
+        ctx.bnhd = bnhd
         if _chunked(q, v):
             o, ctx.kept = _fwd_keep(q, k, v, s)
         else:
-            o = _fwd(q, k, v, sl)
+            o = _fwd(q, k, v, sl, bnhd=bnhd)
         ctx.save_for_backward(q, k, v, s)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, s = ctx.saved_tensors
-        do = do.contiguous()
+        do = _to_layout(do, ctx.bnhd)
         kept, ctx.kept = ctx.kept, None  # usable once: the transposed hand-over changes whose states they are
         if kept is not None:
             return _bwd_from_kept(q, k, v, s, do, kept) + (None,)
         sl = _slopes_arg(s, q.shape[1], q.device)
-        dq, dk, dv = _bwd(q, k, v, sl, do)
+        dq, dk, dv = _bwd(q, k, v, sl, do, bnhd=ctx.bnhd)
         return dq, dk, dv, None
 
 
@@ -215,24 +256,25 @@ class LightningAttention2NoDecay(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v):
         _check_inputs(q, k, v)
-        q = q.contiguous()
-        k = k.contiguous()
-        v = v.contiguous()
+        bnhd = _use_bnhd(q, k, v)
+        q, k, v = (_to_layout(t, bnhd) for t in (q, k, v))
         ctx.kept = None
+        ctx.bnhd = bnhd
         if _chunked(q, v):
             o, ctx.kept = _fwd_keep(q, k, v, None)
         else:
-            o = _fwd(q, k, v, None)
+            o = _fwd(q, k, v, None, bnhd=bnhd)
         ctx.save_for_backward(q, k, v)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v = ctx.saved_tensors
+        do = _to_layout(do, ctx.bnhd)
         kept, ctx.kept = ctx.kept, None
         if kept is not None:
-            return _bwd_from_kept(q, k, v, None, do.contiguous(), kept)
-        dq, dk, dv = _bwd(q, k, v, None, do.contiguous())
+            return _bwd_from_kept(q, k, v, None, do, kept)
+        dq, dk, dv = _bwd(q, k, v, None, do, bnhd=ctx.bnhd)
         return dq, dk, dv
 
 

@@ -475,3 +475,50 @@ def test_decode_step_against_numpy_oracle(cuda_lib):
     assert O.rel_l2_err(f(st), rst) <= 1e-6
     with pytest.raises(RuntimeError):
         la.lightning_attn_decode(q, k, v, s, st.transpose(2, 3))
+
+
+@pytest.mark.parametrize("b,h,n,d,e", [(4, 32, 512, 128, 128), (1, 4, 4096, 128, 128), (2, 3, 300, 64, 96), (1, 8, 2048, 128, 64),
+                                       (2, 12, 384, 192, 192)])
+@pytest.mark.parametrize("decay", [True, False])
+def test_projection_layout_is_read_and_written_in_place(cuda_lib, b, h, n, d, e, decay):
+    """q, k, v given as (b, h, n, d) views of (b, n, h, d) tensors - what rearranging a projection output gives
+    (examples/module/tnl_attn.py:56-59) - are read in place and o, dq, dk, dv come back in the same layout, with exactly
+    the values of the contiguous path (d > 128 falls back to copies and must still agree)."""
+    from lightning_attention_b200.ops.cuda.lightning_attn2 import _is_bnhd
+
+    torch.manual_seed(31)
+    xq, xk = (torch.randn((b, n, h, d), device=DEV).bfloat16().requires_grad_() for _ in range(2))
+    xv = torch.randn((b, n, h, e), device=DEV).bfloat16().requires_grad_()
+    xdo = torch.randn((b, n, h, e), device=DEV).bfloat16()
+    s = la._build_slope_tensor(h).to(DEV) if decay else None
+    o = la.lightning_attn_func(xq.transpose(1, 2), xk.transpose(1, 2), xv.transpose(1, 2), s)
+    o.backward(xdo.transpose(1, 2))
+    if max(d, e) <= 128:
+        assert _is_bnhd(o) and o.transpose(1, 2).is_contiguous()
+    q, k, v = (t.detach().transpose(1, 2).contiguous().requires_grad_() for t in (xq, xk, xv))
+    ro = la.lightning_attn_func(q, k, v, s)
+    ro.backward(xdo.transpose(1, 2).contiguous())
+    assert torch.equal(o, ro)
+    for x, r, name in ((xq, q, "dq"), (xk, k, "dk"), (xv, v, "dv")):
+        assert torch.equal(x.grad.transpose(1, 2), r.grad), name
+    compare_with_torch_reference(q, k, v, xdo.transpose(1, 2).contiguous(), s,
+                                 (o.detach(), xq.grad.transpose(1, 2), xk.grad.transpose(1, 2), xv.grad.transpose(1, 2)), False,
+                                 f"bnhd-{b}-{h}-{n}-{d}-{e}")
+
+
+def test_projection_layout_through_the_c_abi(cuda_lib):
+    """lab200_la_generic with LAB200_LAYOUT_BNHD: forward and reverse time, with states, against the default layout."""
+    torch.manual_seed(32)
+    b, h, n, dk, dv = 2, 3, 640, 64, 128
+    xa, xb = (torch.randn((b, n, h, dk), device=DEV).bfloat16() for _ in range(2))
+    xc = torch.randn((b, n, h, dv), device=DEV).bfloat16()
+    s = (la._build_slope_tensor(h).reshape(-1) * 0.05).to(DEV)
+    st_in = torch.randn((b, h, dv, dk), device=DEV)
+    for reverse in (False, True):
+        for chunks in (1, 3):
+            got, gst = la_generic(xa.transpose(1, 2), xb.transpose(1, 2), xc.transpose(1, 2), s, reverse=reverse, state_in=st_in,
+                                  want_state=True, chunks=chunks)
+            ref, rst = la_generic(xa.transpose(1, 2).contiguous(), xb.transpose(1, 2).contiguous(), xc.transpose(1, 2).contiguous(),
+                                  s, reverse=reverse, state_in=st_in, want_state=True, chunks=chunks)
+            assert got.transpose(1, 2).is_contiguous()
+            assert torch.equal(got, ref) and torch.equal(gst, rst), (reverse, chunks)
