@@ -437,6 +437,24 @@ def main():
         fms, bms = statistics.median(tf), statistics.median(tb)
         srms = {"shape": [M, Nf], "fwd_ms": fms, "bwd_ms": bms, "fwd_gbs": 4.0 * M * Nf / fms / 1e6,
                 "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API (autograd Function); L2 flushed between reps by a 1 GiB memset the launches queue behind"}
+        # the same rows through the fused norm + sigmoid gate (6 and 10 bytes per element)
+        try:
+            gate = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g).requires_grad_()
+            tf, tb = [], []
+            for i in range(8):
+                x.grad = gate.grad = None
+                flush.zero_()
+                a, b_, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                a.record(); y = la.srmsnorm_sigmoid_gate(x, gate); b_.record(); y.backward(dy); c.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    tf.append(a.elapsed_time(b_)); tb.append(b_.elapsed_time(c))
+            gf, gb = statistics.median(tf), statistics.median(tb)
+            srms.update({"gate_fwd_ms": gf, "gate_bwd_ms": gb, "gate_fwd_gbs": 6.0 * M * Nf / gf / 1e6,
+                         "gate_bwd_gbs": 10.0 * M * Nf / gb / 1e6})
+            del gate
+        except Exception as ex:
+            srms["gate_error"] = repr(ex)[:200]
         del x, dy, flush
 
     # ---- projection layout: q, k, v, do as (b, h, n, d) views of (b, n, h, d) tensors, as a caller's projections give them.

@@ -201,6 +201,20 @@ int lab200_srmsnorm_fwd(const void* x, void* y, float* rstd, long long M, int N,
 int lab200_srmsnorm_bwd(const void* x, const void* dy, const float* rstd, void* dx, long long M, int N,
                         int dtype, void* stream);
 
+/*
+ * SimpleRMSNorm followed by a sigmoid gate in one pass, the epilogue of the reference's example caller
+ * (examples/module/tnl_attn.py:66-69: norm, sigmoid(gate), multiply - with this repo's SimpleRMSNorm as the norm):
+ *   forward : y = x * rstd * sigmoid(gate)
+ *   backward: dx and dgate from dy (see csrc/srmsnorm_kernels.cuh)
+ * x, gate, y, dy, dx, dgate: (M, N) row-major of one dtype; rstd: (M) fp32. Rows must be vectorisable: N a multiple of
+ * 8 (16-bit) or 4 (fp32) and at most 16384 / 8192 elements, pointers 16-byte aligned; LAB200_ERR_SHAPE / _ALIGN otherwise
+ * (compose lab200_srmsnorm_* with element-wise kernels then). No counterpart kernel in the reference.
+ */
+int lab200_srmsnorm_gate_fwd(const void* x, const void* gate, void* y, float* rstd, long long M, int N, float eps,
+                             int dtype, void* stream);
+int lab200_srmsnorm_gate_bwd(const void* x, const void* gate, const void* dy, const float* rstd, void* dx,
+                             void* dgate, long long M, int N, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -47,6 +47,10 @@ def lib():
         L.lab200_la_combine_states.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, ctypes.c_longlong, i, vp]
         L.lab200_la_decode_step.restype = i
         L.lab200_la_decode_step.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp]
+        L.lab200_srmsnorm_gate_fwd.restype = i
+        L.lab200_srmsnorm_gate_fwd.argtypes = [vp, vp, vp, vp, ll, i, f, i, vp]
+        L.lab200_srmsnorm_gate_bwd.restype = i
+        L.lab200_srmsnorm_gate_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ll, i, i, vp]
         L.lab200_la2_fwd.restype = i
         L.lab200_la2_fwd.argtypes = [vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, vp]
         L.lab200_la2_fwd_static.restype = i
@@ -68,7 +72,7 @@ def lib():
 EXPORTS = [
     "lab200_version", "lab200_launch_count", "lab200_la_debug_trace", "lab200_error_string", "lab200_la_plan_chunks", "lab200_la_workspace_bytes",
     "lab200_la_generic", "lab200_la_generic_resume", "lab200_la_generic_resume_swapped", "lab200_la_combine_states", "lab200_la_decode_step", "lab200_la2_fwd", "lab200_la2_fwd_static", "lab200_la2_bwd", "lab200_la2_dkdv", "lab200_read_status",
-    "lab200_srmsnorm_fwd", "lab200_srmsnorm_bwd",
+    "lab200_srmsnorm_fwd", "lab200_srmsnorm_bwd", "lab200_srmsnorm_gate_fwd", "lab200_srmsnorm_gate_bwd",
 ]
 
 

@@ -472,6 +472,51 @@ int srms_dispatch(bool fwd, const void* x, const void* dy, void* out, float* rst
   return LAB200_ERR_SHAPE;
 }
 
+// Gated SRMSNorm: vectorised rows only (row length a multiple of the vector width, 16-byte aligned pointers, at most
+// 2048 vectors so that three rows' worth of registers fit); callers compose the plain kernels otherwise.
+template <int DT, int G, int VPT>
+void srms_gate_launch(bool fwd, const void* x, const void* g, const void* dy, void* out, void* dg, float* rstd, long long M,
+                      int N, float eps, cudaStream_t st) {
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  const unsigned grid = static_cast<unsigned>((M + RPC - 1) / RPC);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (fwd) srmsnorm_gate_fwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, g, out, rstd, static_cast<int>(M), N, eps);
+  else srmsnorm_gate_bwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, g, dy, rstd, out, dg, static_cast<int>(M), N);
+}
+
+template <int DT>
+int srms_gate_dispatch(bool fwd, const void* x, const void* g, const void* dy, void* out, void* dg, float* rstd, long long M,
+                       int N, float eps, cudaStream_t st) {
+  constexpr int EPV = SrmsVec<DT>::EPV;
+  if ((N % EPV) != 0) return LAB200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(g) || !aligned16(out) || (!fwd && (!aligned16(dy) || !aligned16(dg)))) return LAB200_ERR_ALIGN;
+  const int nvec = N / EPV;
+#define LAB200_SRMSG(G, V) \
+  if (nvec <= G * V) { srms_gate_launch<DT, G, V>(fwd, x, g, dy, out, dg, rstd, M, N, eps, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
+  LAB200_SRMSG(32, 2)
+  LAB200_SRMSG(32, 4)
+  LAB200_SRMSG(128, 2)
+  LAB200_SRMSG(128, 4)
+  LAB200_SRMSG(256, 4)
+  LAB200_SRMSG(512, 4)
+#undef LAB200_SRMSG
+  return LAB200_ERR_SHAPE;
+}
+
+int srms_gate_entry(bool fwd, const void* x, const void* g, const void* dy, void* out, void* dg, float* rstd, long long M,
+                    int N, float eps, int dtype, cudaStream_t st) {
+  if (M < 0 || N < 1 || M > 2147483647LL) return LAB200_ERR_SHAPE;
+  if (!x || !g || !out || !rstd || (!fwd && (!dy || !dg))) return M == 0 ? LAB200_OK : LAB200_ERR_SHAPE;
+  if (M == 0) return LAB200_OK;
+  switch (dtype) {
+    case LAB200_F32: return srms_gate_dispatch<SRMS_F32>(fwd, x, g, dy, out, dg, rstd, M, N, eps, st);
+    case LAB200_F16: return srms_gate_dispatch<SRMS_F16>(fwd, x, g, dy, out, dg, rstd, M, N, eps, st);
+    case LAB200_BF16: return srms_gate_dispatch<SRMS_BF16>(fwd, x, g, dy, out, dg, rstd, M, N, eps, st);
+    default: return LAB200_ERR_DTYPE;
+  }
+}
+
 int srms_entry(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
                int dtype, cudaStream_t st) {
   if (M < 0 || N < 1 || M > 2147483647LL) return LAB200_ERR_SHAPE;
@@ -723,6 +768,17 @@ int lab200_srmsnorm_fwd(const void* x, void* y, float* rstd, long long M, int N,
 int lab200_srmsnorm_bwd(const void* x, const void* dy, const float* rstd, void* dx, long long M, int N, int dtype,
                         void* stream) {
   return srms_entry(false, x, dy, dx, const_cast<float*>(rstd), M, N, 0.f, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int lab200_srmsnorm_gate_fwd(const void* x, const void* gate, void* y, float* rstd, long long M, int N, float eps,
+                             int dtype, void* stream) {
+  return srms_gate_entry(true, x, gate, nullptr, y, nullptr, rstd, M, N, eps, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int lab200_srmsnorm_gate_bwd(const void* x, const void* gate, const void* dy, const float* rstd, void* dx, void* dgate,
+                             long long M, int N, int dtype, void* stream) {
+  return srms_gate_entry(false, x, gate, dy, dx, dgate, const_cast<float*>(rstd), M, N, 0.f, dtype,
+                         static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

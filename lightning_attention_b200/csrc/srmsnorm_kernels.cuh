@@ -192,6 +192,122 @@ srmsnorm_bwd_kernel(const void* __restrict__ x_, const void* __restrict__ dy_, c
   }
 }
 
+// Gated form used by callers that multiply the normalised output by a sigmoid gate (examples/module/tnl_attn.py:66-69):
+//   forward : y = x * rstd * sigmoid(g)                                              6 bytes per 16-bit element
+//   backward: sg = sigmoid(g); xhat = x * rstd; t = dy * sg; c = mean(xhat * t);
+//             dx = (t - xhat * c) * rstd;  dg = dy * xhat * sg * (1 - sg)           10 bytes per element
+// One pass each instead of norm + sigmoid + multiply as three kernels (14 and 26 bytes per element).
+__device__ __forceinline__ float sigmoidf_fast(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
+
+template <int DT, int G, int VPT>
+__global__ void __launch_bounds__((G > 256 ? G : 256))
+srmsnorm_gate_fwd_kernel(const void* __restrict__ x_, const void* __restrict__ g_, void* __restrict__ y_,
+                         float* __restrict__ rstd_, int M, int N, float eps) {
+  using V = SrmsVec<DT>;
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  __shared__ float red[RPC][16];
+  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
+  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
+  const bool active = row < M;
+  const int nvec = N / V::EPV;
+  const size_t off = static_cast<size_t>(active ? row : 0) * nvec;
+  const uint4* x = reinterpret_cast<const uint4*>(x_) + off;
+  const uint4* g = reinterpret_cast<const uint4*>(g_) + off;
+  uint4* y = reinterpret_cast<uint4*>(y_) + off;
+
+  uint4 xv[VPT], gv[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      xv[i] = ld_stream(x + v);
+      gv[i] = ld_stream(g + v);
+      float f[V::EPV];
+      V::unpack(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+  }
+  ss = group_sum<G>(ss, red[grp], tig);
+  const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
+  if (active && tig == 0) rstd_[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      float f[V::EPV], fg[V::EPV];
+      V::unpack(xv[i], f);
+      V::unpack(gv[i], fg);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) f[j] = f[j] * rstd * sigmoidf_fast(fg[j]);
+      st_stream(y + v, V::pack(f));
+    }
+  }
+}
+
+template <int DT, int G, int VPT>
+__global__ void __launch_bounds__((G > 256 ? G : 256))
+srmsnorm_gate_bwd_kernel(const void* __restrict__ x_, const void* __restrict__ g_, const void* __restrict__ dy_,
+                         const float* __restrict__ rstd_, void* __restrict__ dx_, void* __restrict__ dg_, int M, int N) {
+  using V = SrmsVec<DT>;
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  __shared__ float red[RPC][16];
+  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
+  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
+  const bool active = row < M;
+  const int nvec = N / V::EPV;
+  const size_t off = static_cast<size_t>(active ? row : 0) * nvec;
+  const uint4* x = reinterpret_cast<const uint4*>(x_) + off;
+  const uint4* g = reinterpret_cast<const uint4*>(g_) + off;
+  const uint4* dy = reinterpret_cast<const uint4*>(dy_) + off;
+  uint4* dx = reinterpret_cast<uint4*>(dx_) + off;
+  uint4* dg = reinterpret_cast<uint4*>(dg_) + off;
+  const float rstd = active ? rstd_[row] : 0.f;
+
+  uint4 xv[VPT], gv[VPT], dv[VPT];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      xv[i] = ld_stream(x + v);
+      gv[i] = ld_stream(g + v);
+      dv[i] = ld_stream(dy + v);
+      float fx[V::EPV], fg[V::EPV], fd[V::EPV];
+      V::unpack(xv[i], fx);
+      V::unpack(gv[i], fg);
+      V::unpack(dv[i], fd);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fd[j] * sigmoidf_fast(fg[j]), dot);
+    }
+  }
+  dot = group_sum<G>(dot, red[grp], tig);
+  const float c = dot / static_cast<float>(N);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nvec) {
+      float fx[V::EPV], fg[V::EPV], fd[V::EPV];
+      V::unpack(xv[i], fx);
+      V::unpack(gv[i], fg);
+      V::unpack(dv[i], fd);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) {
+        const float sg = sigmoidf_fast(fg[j]);
+        const float xh = fx[j] * rstd;
+        const float t = fd[j] * sg;
+        fg[j] = fd[j] * xh * sg * (1.0f - sg);  // dg
+        fx[j] = (t - xh * c) * rstd;            // dx
+      }
+      st_stream(dx + v, V::pack(fx));
+      st_stream(dg + v, V::pack(fg));
+    }
+  }
+}
+
 // Fallback for rows whose length or base address does not allow 128-bit vectors: one 256-thread
 // CTA per row, element-wise loads, the row is read twice (the second read normally hits L2).
 template <int DT> struct SrmsElem;

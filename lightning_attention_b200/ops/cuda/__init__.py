@@ -8,4 +8,4 @@ from .lightning_attn2 import (  # noqa: F401
     lightning_attn_prefill,
     lightning_attn_decode,
 )
-from .srmsnorm import SimpleRMSNorm, _SrmsNorm  # noqa: F401
+from .srmsnorm import SimpleRMSNorm, _SrmsNorm, srmsnorm_sigmoid_gate  # noqa: F401

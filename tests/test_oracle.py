@@ -151,3 +151,19 @@ def test_state_and_decode_chain_matches_definition():
         o, st = O.decode_step(q[:, :, t], k[:, :, t], v[:, :, t], s, st)
         outs.append(o[:, :, None])
     assert O.max_abs_err(np.concatenate(outs, axis=2), ref) < 1e-10
+
+
+def test_gated_norm_gradients_match_autograd():
+    """oracle.srmsnorm_gate_* against torch autograd of SimpleRMSNorm(x) * sigmoid(g) in fp64 on the CPU."""
+    import torch
+
+    rng = np.random.default_rng(6)
+    x, g, dy = rng.standard_normal((3, 5, 64))
+    xt, gt = (torch.tensor(t, dtype=torch.float64, requires_grad=True) for t in (x, g))
+    y = xt * torch.rsqrt(xt.pow(2).mean(-1, keepdim=True) + 1e-6) * torch.sigmoid(gt)
+    y.backward(torch.tensor(dy))
+    oy, _ = O.srmsnorm_gate_fwd(x, g)
+    dx, dg = O.srmsnorm_gate_bwd(x, g, dy)
+    assert O.max_abs_err(oy, y.detach().numpy()) < 1e-12
+    assert O.max_abs_err(dx, xt.grad.numpy()) < 1e-12
+    assert O.max_abs_err(dg, gt.grad.numpy()) < 1e-12

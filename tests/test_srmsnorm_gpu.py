@@ -110,3 +110,38 @@ def test_fp16_eps_clamp_and_determinism(cuda_lib):
     assert torch.isfinite(y).all() and float(y.abs().max()) == 0.0
     x = torch.randn((64, 4096), dtype=torch.bfloat16, device=DEV)
     assert torch.equal(la.SimpleRMSNorm(4096)(x), la.SimpleRMSNorm(4096)(x))
+
+
+@pytest.mark.parametrize("shape", [(4, 1024, 1024), (2, 257, 768), (8192, 4096), (3, 16384), (5, 64), (2, 100), (3, 24576)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_norm_with_sigmoid_gate(cuda_lib, shape, dtype):
+    """SimpleRMSNorm(x) * sigmoid(gate), fused forward and backward, against the same expression in fp32 torch with
+    autograd; (2, 100) and (3, 24576) take the composed path (rows not vectorisable / too long for the fused kernel)."""
+    torch.manual_seed(2025)
+    x, g = (torch.randn(shape, dtype=dtype, device=DEV).requires_grad_() for _ in range(2))
+    dy = torch.randn(shape, dtype=dtype, device=DEV)
+    if shape[-1] * x.element_size() > 65536:  # the norm's own row limit (srmsnorm.py:94-97) applies to the composed path
+        with pytest.raises(RuntimeError, match="64KB"):
+            la.srmsnorm_sigmoid_gate(x, g)
+        return
+    y = la.srmsnorm_sigmoid_gate(x, g)
+    y.backward(dy)
+    xr, gr = (t.detach().float().requires_grad_() for t in (x, g))
+    yr = la.SimpleRMSNormTorch(shape[-1])(xr) * torch.sigmoid(gr)
+    yr.backward(dy.float())
+    assert y.dtype == dtype and y.shape == x.shape
+    assert_close(y.float(), yr, atol=ATOL, rtol=RTOL)
+    assert_close(x.grad.float(), xr.grad, atol=ATOL, rtol=RTOL)
+    assert_close(g.grad.float(), gr.grad, atol=ATOL, rtol=RTOL)
+
+
+def test_norm_with_sigmoid_gate_against_numpy_oracle(cuda_lib):
+    torch.manual_seed(2026)
+    x, g, dy = (torch.randn((6, 512), dtype=torch.float32, device=DEV) for _ in range(3))
+    x.requires_grad_(); g.requires_grad_()
+    y = la.srmsnorm_sigmoid_gate(x, g)
+    y.backward(dy)
+    f = lambda t: t.detach().cpu().numpy()
+    oy, _ = O.srmsnorm_gate_fwd(f(x), f(g))
+    dx, dg = O.srmsnorm_gate_bwd(f(x), f(g), f(dy))
+    assert O.rel_l2_err(f(y), oy) < 1e-5 and O.rel_l2_err(f(x.grad), dx) < 1e-5 and O.rel_l2_err(f(g.grad), dg) < 1e-5
