@@ -400,6 +400,11 @@ int la_dkdv_impl(const void* q, const void* k, const void* v, const void* dout, 
   return LAB200_ERR_SHAPE;
 }
 
+// A reverse-time sweep starts in the last block; the state arriving there is taken to sit at the end of a full tile.
+bool reverse_chain_ok(int reverse, const float* state_in, int n) {
+  return !(reverse && state_in != nullptr && (n % LA_BLOCK) != 0);
+}
+
 // Argument checks that need no CUDA call; run before anything is enqueued.
 int la_validate(const void* a, const void* bm, const void* c, const void* out, const float* state_in,
                 const float* state_out, const void* workspace, int bh, int h, int n, int dk, int dv, int state_only,
@@ -611,6 +616,7 @@ int lab200_la_generic(const void* a, const void* bm, const void* c, const float*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = la_validate(a, bm, c, out, state_in, state_out, workspace, bh, h, n, dk, dv, state_only, dtype);
   if (rc != LAB200_OK) return rc;
+  if (!reverse_chain_ok(reverse, state_in, n)) return LAB200_ERR_SHAPE;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
   return la_generic_impl(a, bm, c, slopes, out, state_in, state_out, workspace, workspace_bytes, bh, h, n, dk, dv,
                          reverse, state_only, chunks, dtype, st);
@@ -622,6 +628,7 @@ int lab200_la_generic_resume(const void* a, const void* bm, const void* c, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = la_validate(a, bm, c, out, state_in, nullptr, workspace, bh, h, n, dk, dv, 0, dtype);
   if (rc != LAB200_OK) return rc;
+  if (!reverse_chain_ok(reverse, state_in, n)) return LAB200_ERR_SHAPE;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
   return la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
                          chunks, dtype, st, RESUME);
@@ -634,6 +641,7 @@ int lab200_la_generic_resume_swapped(const void* a, const void* bm, const void* 
   if (dk != dv) return LAB200_ERR_SHAPE;
   int rc = la_validate(a, bm, c, out, state_in, nullptr, workspace, bh, h, n, dk, dv, 0, dtype);
   if (rc != LAB200_OK) return rc;
+  if (!reverse_chain_ok(reverse, state_in, n)) return LAB200_ERR_SHAPE;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
   return la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
                          chunks, dtype, st, RESUME | RESUME_SWAPPED | (rebase ? 0 : RESUME_NO_REBASE));

@@ -58,6 +58,11 @@ def test_attention_argument_validation_needs_no_gpu():
     assert L.lab200_la_generic(p + 2, p, p, None, p, None, None, p, ws, 1, 1, 128, 64, 64, 0, 0, 0, _lib.BF16, None) == 6
     assert L.lab200_la_generic(p, p, p, None, p, None, None, p, ws, 0, 1, 128, 64, 64, 0, 0, 0, _lib.BF16, None) == 1
     assert L.lab200_la2_fwd(p, p, p, None, p, p, ws, 1, 1, 0, 64, 64, 0, _lib.BF16, None) == 1
+    # a reverse-time sweep cannot take an incoming state when the sequence ends in a ragged block
+    assert L.lab200_la_generic(p, p, p, None, p, p, None, p, ws, 1, 1, 200, 64, 64, 1, 0, 0, _lib.BF16, None) == 1
+    # the projection-layout flag needs whole batches of heads and dk <= 128
+    assert L.lab200_la_generic(p, p, p, None, p, None, None, p, ws, 3, 2, 128, 64, 64, 0, 0, 0, _lib.BF16 | 0x100, None) == 1
+    assert L.lab200_la_generic(p, p, p, None, p, None, None, p, ws, 2, 2, 128, 192, 64, 0, 0, 0, _lib.BF16 | 0x100, None) == 1
     assert L.lab200_la2_bwd(p, p, p, None, p, p, p, p, p, ws, 1, 1, 128, 64, 20, 0, _lib.BF16, None) == 1
 
 
