@@ -522,3 +522,43 @@ def test_projection_layout_through_the_c_abi(cuda_lib):
                                   s, reverse=reverse, state_in=st_in, want_state=True, chunks=chunks)
             assert got.transpose(1, 2).is_contiguous()
             assert torch.equal(got, ref) and torch.equal(gst, rst), (reverse, chunks)
+
+
+def _random_case(seed):
+    rng = np.random.default_rng(1000 + seed)
+    b = int(rng.integers(1, 4))
+    h = int(rng.integers(1, 6))
+    n = int(rng.integers(1, 900))
+    dk = 16 * int(rng.integers(1, 17))
+    dv = 16 * int(rng.integers(1, 17))
+    reverse = bool(rng.integers(0, 2))
+    chunks = int(rng.choice([0, 1, 2, 5]))
+    layout = bool(rng.integers(0, 2)) and dk <= 128 and dv <= 128
+    with_state = bool(rng.integers(0, 2)) and not (reverse and n % 128)
+    slope_scale = float(rng.choice([0.0, 0.02, 1.0]))
+    return b, h, n, dk, dv, reverse, chunks, layout, with_state, slope_scale
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_randomised_shapes_against_numpy_oracle(cuda_lib, seed):
+    """Seeded random draws over batch, heads, length, feature dims (16..256), direction, chunking, layout, incoming state
+    and decay strength; output and outgoing state against the numpy oracle."""
+    b, h, n, dk, dv, reverse, chunks, layout, with_state, slope_scale = _random_case(seed)
+    torch.manual_seed(seed)
+    if layout:
+        a, bm = (torch.randn((b, n, h, dk), device=DEV).bfloat16().transpose(1, 2) for _ in range(2))
+        c = torch.randn((b, n, h, dv), device=DEV).bfloat16().transpose(1, 2)
+    else:
+        a, bm = (torch.randn((b, h, n, dk), device=DEV).bfloat16() for _ in range(2))
+        c = torch.randn((b, h, n, dv), device=DEV).bfloat16()
+    s = (la._build_slope_tensor(h).reshape(-1) * slope_scale).to(DEV) if slope_scale > 0 else None
+    st_in = torch.randn((b, h, dv, dk), device=DEV) if with_state else None
+    want_state = (not reverse) or n % 128 == 0
+    out, st = la_generic(a, bm, c, s, reverse=reverse, state_in=st_in, want_state=want_state, chunks=chunks)
+    f = lambda t: None if t is None else t.float().cpu().numpy()
+    ro, rs = O.la_generic(f(a), f(bm), f(c), f(s), reverse=reverse, state_in=f(st_in))
+    tag = str(_random_case(seed))
+    assert O.rel_l2_err(f(out), ro) <= 1e-2, tag
+    assert O.max_abs_err(f(out), ro) <= 2e-2 * max(1.0, float(np.abs(ro).max())), tag
+    if want_state:
+        assert O.rel_l2_err(f(st), rs) <= 1e-2, tag
