@@ -10,8 +10,14 @@ With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same wor
 (batch, head) units with no communication (weak scaling); the value is the sum over ranks divided by
 the slowest rank's time.
 
-Rank 0 prints ONE JSON line. `--impl reference` times the CPU restatement of the reference's
-recurrences (oracle/) on the host cores instead, on a bounded sample of the same workload.
+Rank 0 prints ONE JSON line. Beside the headline it carries, untimed by the headline: the roofline of the block kernels,
+SRMSNorm (both shapes of the norm benchmark config), the README example shape (d = e = 192), the reference's whole sweep
+over n with and without decay, a sustained (>= 2 s) run of the headline step, the (batch, head)-sharded step at fixed total
+work (`bh_strong`), the sequence-parallel long-context leg with its parity checks at every N > 1 (`long_context`), the
+end-to-end step from pinned host buffers, and two CPU baselines (the numpy port of the block recurrences at n = 32768 and
+the reference's naive O(n^2) torch path where it fits in memory).
+`--impl reference` times the CPU restatement of the reference's recurrences (oracle/) on the host cores instead, on a
+bounded sample of the same workload.
 """
 import argparse
 import json
@@ -31,9 +37,13 @@ SEED = 2024
 # (read q,k,v / write o; read q,k,v,do / write dq,dk,dv) and flops with the reference's 64-token blocks.
 ALG_BYTES_PER_UNIT = 2816
 ALG_FLOP_PER_UNIT = 344064
-LA_LAUNCHES_PER_STEP = 4  # generic-product equivalents per step: o, dq, dk, dv (dk and dv share one fused launch)
-# DRAM bytes (read + write) per launch of la_chunk_kernel measured with ncu; see profiles/. None = not captured yet.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 4 * 1048.7e6  # n=8192 capture (1048.7 MB) scaled x4: traffic is linear in n
+# Block-kernel launches per step: o and dq are one launch of the generic product each, dk and dv share one fused sweep.
+LA_LAUNCHES_PER_STEP = 3
+# Tensor passes (one pass = one (b, h, n, 128) bf16 tensor read or written once) the three launches move: 4 + 4 + 6,
+# against the 11 that are compulsory. DRAM bytes per pass measured with ncu on la_pipe_kernel at n = 8192: 1048.7 MB per
+# 4-pass launch, i.e. 1.0x of what the launch must move (see profiles/); traffic is linear in n.
+PASSES_MOVED_PER_STEP = 14
+NCU_BYTES_PER_PASS_N8192 = 1048.7e6 / 4
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -306,6 +316,473 @@ def run_trace(emit):
                          "offsets_cycles": {name: round(x) for name, x in zip(TRACE_SLOTS, rel)}}))
 
 
+
+# ------------------------------------------------------------------------------------------------------------------
+# legs of the bench line (all untimed by the headline; each returns a small dict)
+# ------------------------------------------------------------------------------------------------------------------
+def numa_pin(local_rank):
+    """Restrict this process to the CPUs of the NUMA node its GPU hangs off, before any pinned host buffer is
+    allocated, so that cudaHostAlloc's pages are node-local to the GPU's PCIe root complex (first-touch policy).
+    Read-only NVML / sysfs queries plus os.sched_setaffinity on this process only."""
+    info = {"numa_node": None}
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(local_rank)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bus = bus.lower()
+        if len(bus.split(":")[0]) == 8:  # NVML prints an 8-digit PCI domain, sysfs a 4-digit one
+            bus = bus[4:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        info["numa_node"] = node
+        if node >= 0:
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                cpus = set()
+                for part in f.read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = cpus & set(os.sched_getaffinity(0))
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                info["cpus_on_node"] = len(allowed)
+    except Exception as ex:
+        info["note"] = "affinity left unchanged: " + repr(ex)[:120]
+    return info
+
+
+def event_time(torch, fn, reps, warm=3):
+    """Mean device milliseconds of fn() over `reps` back-to-back calls inside ONE event pair."""
+    for _ in range(warm):
+        fn()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(reps):
+        fn()
+    b_.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b_) / reps
+
+
+def leg_srmsnorm(torch, la, L, dev, g, M, Nf, with_gate):
+    """SimpleRMSNorm fwd / bwd on (M, Nf) bf16. Two timings: through the autograd Function with one event pair per call and
+    the L2 flushed in between (what a user sees, host launch gaps included), and 20 back-to-back launches of each kernel
+    through the C ABI inside one event pair (device time of the kernel; x, y, dy, dx far exceed L2, so nothing is reused)."""
+    from lightning_attention_b200 import _lib
+
+    x = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g).requires_grad_()
+    dy = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g)
+    norm = la.SimpleRMSNorm(Nf)
+    flush = torch.empty(1024 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    tf, tb = [], []
+    for i in range(8):
+        x.grad = None
+        flush.zero_()
+        a, b_, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record(); y = norm(x); b_.record(); y.backward(dy); c.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            tf.append(a.elapsed_time(b_)); tb.append(b_.elapsed_time(c))
+    fms, bms = statistics.median(tf), statistics.median(tb)
+    out = {"shape": [M, Nf], "fwd_ms": fms, "bwd_ms": bms, "fwd_gbs": 4.0 * M * Nf / fms / 1e6, "bwd_gbs": 6.0 * M * Nf / bms / 1e6,
+           "note": "fwd_ms / bwd_ms: public API (autograd Function), one event pair per call, L2 flushed by a 1 GiB memset the "
+                   "launches queue behind; kernel_*: 20 back-to-back C-ABI launches per event pair"}
+    # the kernels alone
+    xd = x.detach()
+    yk = torch.empty_like(xd)
+    dxk = torch.empty_like(xd)
+    rstd = torch.empty((M,), dtype=torch.float32, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    kf = event_time(torch, lambda: L.lab200_srmsnorm_fwd(xd.data_ptr(), yk.data_ptr(), rstd.data_ptr(), M, Nf, 1e-6, _lib.BF16, st), 20)
+    kb = event_time(torch, lambda: L.lab200_srmsnorm_bwd(xd.data_ptr(), dy.data_ptr(), rstd.data_ptr(), dxk.data_ptr(), M, Nf, _lib.BF16, st), 20)
+    out.update({"kernel_fwd_ms": kf, "kernel_bwd_ms": kb, "kernel_fwd_gbs": 4.0 * M * Nf / kf / 1e6, "kernel_bwd_gbs": 6.0 * M * Nf / kb / 1e6})
+    del yk, dxk
+    if with_gate:
+        try:
+            gate = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g).requires_grad_()
+            tf, tb = [], []
+            for i in range(8):
+                x.grad = gate.grad = None
+                flush.zero_()
+                a, b_, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                a.record(); y = la.srmsnorm_sigmoid_gate(x, gate); b_.record(); y.backward(dy); c.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    tf.append(a.elapsed_time(b_)); tb.append(b_.elapsed_time(c))
+            gf, gb = statistics.median(tf), statistics.median(tb)
+            out.update({"gate_fwd_ms": gf, "gate_bwd_ms": gb, "gate_fwd_gbs": 6.0 * M * Nf / gf / 1e6, "gate_bwd_gbs": 10.0 * M * Nf / gb / 1e6})
+        except Exception as ex:
+            out["gate_error"] = repr(ex)[:200]
+    return out
+
+
+def leg_config2(torch, la, dev, hbm_peak):
+    """The README example shape: b=2, h=12, n=2048, d=e=192 bf16, fwd and bwd of o.sum() separately, with its own HBM roofline
+    (4224 B and 688,128 flop per (token, head): 2 * (2d + 2e) + 2 * (2d + 2e) + 2 * (2d + e) at d = e = 192)."""
+    b, h, n, d = 2, 12, 2048, 192
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED)
+    q, k, v = (torch.randn((b, h, n, d), device=dev, generator=g).to(torch.bfloat16).requires_grad_() for _ in range(3))
+    do = torch.ones((b, h, n, d), device=dev, dtype=torch.bfloat16)  # gradient of o.sum()
+    s = torch.tensor([2.0 ** (-8.0 * (i + 1) / h) for i in range(h)], device=dev).reshape(h, 1, 1)
+    fwd = event_time(torch, lambda: la.lightning_attn_func(q, k, v, s), 20, warm=5)
+    o = la.lightning_attn_func(q, k, v, s)
+
+    def bwd_fn():
+        q.grad = k.grad = v.grad = None
+        o.backward(do, retain_graph=True)
+
+    bwd = event_time(torch, bwd_fn, 20, warm=5)
+    units = b * h * n
+    gbs = 4224.0 * units / ((fwd + bwd) * 1e-3) / 1e9
+    return {"shape": [b, h, n, d, d], "fwd_ms": fwd, "bwd_ms": bwd, "tokens_per_s": b * n / ((fwd + bwd) * 1e-3),
+            "alg_gbs": gbs, "hbm_frac": gbs / hbm_peak, "alg_tflops": 688128.0 * units / ((fwd + bwd) * 1e-3) / 1e12,
+            "note": "20 back-to-back calls per event pair; the 4 x 18.9 MB working set fits L2, so this is a latency/occupancy "
+                    "figure (24 (batch, head) pairs on 148 SMs: chunk mode), not a DRAM one"}
+
+
+def leg_sweep(torch, la, dev, s):
+    """The reference's speed table (benchmarks/benchmark_lightning2.py:56-118): b4 h32 d=e=128 bf16, n = 512 ... 32768, with
+    and without decay, fwd and bwd separately; medians of 7 event-timed calls after 3 warm-ups, L2 flushed between calls.
+    Compact form: [n, fwd_ms, bwd_ms, published fwd_ms, published bwd_ms] (published: README.md:58-76 for decay,
+    benchmarks/README.md:52-69 for no decay; hardware not stated there)."""
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=7, warm=3):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b_.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b_))
+        return statistics.median(ts)
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED)
+    rows = {"decay": [], "no_decay": []}
+    for n in (512, 1024, 2048, 4096, 8192, 16384, 32768):
+        q, k, v = (torch.randn((B, H, n, D), device=dev, generator=g).to(torch.bfloat16).requires_grad_() for _ in range(3))
+        do = torch.randn((B, H, n, D), device=dev, generator=g).to(torch.bfloat16)
+        for name, fn, ref_f, ref_b in (("decay", lambda: la.lightning_attn2(q, k, v, s), REF_LIGHTNING2_FWD, REF_LIGHTNING2_BWD),
+                                       ("no_decay", lambda: la.lightning_attn2_no_decay(q, k, v), REF_NODECAY_FWD, REF_NODECAY_BWD)):
+            fwd = timed(fn)
+            o = fn()
+
+            def bwd_fn():
+                q.grad = k.grad = v.grad = None
+                o.backward(do, retain_graph=True)
+
+            bwd = timed(bwd_fn)
+            del o
+            q.grad = k.grad = v.grad = None
+            rows[name].append([n, round(fwd, 4), round(bwd, 4), round(ref_f[n], 4), round(ref_b[n], 4)])
+        del q, k, v, do
+    rows["columns"] = ["n", "fwd_ms", "bwd_ms", "published_fwd_ms", "published_bwd_ms"]
+    return rows
+
+
+def leg_sustained(torch, step, seconds, sampler_index):
+    """>= `seconds` of back-to-back headline steps in one event pair, SM clocks sampled through NVML meanwhile: the
+    power / thermal steady state the 20-step headline window does not reach."""
+    ms_guess = event_time(torch, step, 3, warm=1)
+    reps = max(10, int(seconds * 1e3 / ms_guess) + 1)
+    sampler = ClockSampler(sampler_index)
+    sampler.start()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(reps):
+        step()
+    b_.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = a.elapsed_time(b_) / reps
+    return {"steps": reps, "seconds": a.elapsed_time(b_) * 1e-3, "ms_per_step": ms, "tokens_per_s": B * N_TOK / (ms * 1e-3),
+            "hbm_frac": ALG_BYTES_PER_UNIT * B * H * N_TOK / (ms * 1e-3) / 1e9 / load_peaks()[0], "clocks": clocks}
+
+
+def leg_bh_strong(torch, dist, la, dev, rank, world, q, k, v, do, s, t1_ms):
+    """Batch x heads sharding at FIXED total work: the 128 (batch, head) pairs of the headline step split contiguously over
+    the ranks (128 / N pairs per GPU, no collective). Every rank holds the same seeded tensors here only so that it can
+    slice its share; a real job would hold just the share. t1_ms: the single-GPU time of the whole step (the headline)."""
+    from lightning_attention_b200 import distributed as la_dist
+    from lightning_attention_b200.ops.cuda.lightning_attn2 import la_generic
+
+    q_l, k_l, v_l, s_l = la_dist.bh_shard(q.detach(), k.detach(), v.detach(), s, rank, world)
+    do_l = la_dist.bh_shard(do, do, do, None, rank, world)[0]
+    q_l, k_l, v_l = (t.contiguous().requires_grad_() for t in (q_l, k_l, v_l))
+    do_l = do_l.contiguous()
+
+    def step():
+        q_l.grad = k_l.grad = v_l.grad = None
+        la.lightning_attn2(q_l, k_l, v_l, s_l).backward(do_l)
+
+    ms = event_time(torch, step, 20)
+    # share of the chunk-mode overhead: the two state-only passes (k, v) and (do, q) with their scans
+    st_ms = event_time(torch, lambda: (la_generic(None, k_l.detach(), v_l.detach(), s_l, state_only=True),
+                                       la_generic(None, do_l, q_l.detach(), s_l, reverse=True, state_only=True)), 10)
+    t = torch.tensor([ms, st_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, st_ms = float(t[0]), float(t[1])
+    pairs = q_l.shape[1]
+    from lightning_attention_b200 import _lib
+    with torch.cuda.device(dev):
+        chunks = _lib.lib().lab200_la_plan_chunks(pairs, N_TOK, D, D)
+    return {"pairs_per_gpu": pairs, "chunks_per_pair": chunks, "ms_per_step": ms, "tokens_per_s": B * N_TOK / (ms * 1e-3),
+            "t1_ms": t1_ms, "efficiency": t1_ms / (world * ms), "state_passes_ms": st_ms, "state_passes_share": st_ms / ms,
+            "note": "fixed total work b4 h32 n32768 split over the ranks; efficiency = T_1 / (N T_N) with T_1 = this run's "
+                    "single-GPU step time on the whole problem; state_passes = the two state-only launches + scans that "
+                    "chunk mode adds (max over ranks)"}
+
+
+def _rel_l2(torch, x, ref):
+    x, ref = x.float(), ref.float()
+    den = float(ref.norm())
+    return float((x - ref).norm()) / den if den > 0 else float((x - ref).norm())
+
+
+def _decay_variants(la, dev):
+    s = la._build_slope_tensor(H).to(dev)
+    return (("alibi", s), ("alibi_x1e-3", s * 1e-3), ("no_decay", None))
+
+
+def sp_parity_small(torch, dist, la, la_dist, dev, rank, world, Ls=8192):
+    """Every rank computes the single-GPU fwd+bwd on the whole sequence (n = world * Ls) and compares its shard of o, dq, dk,
+    dv with what the sequence-parallel op returns: rel-L2, max over ranks, per decay variant."""
+    n = world * Ls
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED + 77)  # same seed on every rank: identical full tensors
+    full = [(0.5 * torch.randn((1, H, n, D), device=dev, generator=g)).to(torch.bfloat16) for _ in range(4)]
+    sl = slice(rank * Ls, (rank + 1) * Ls)
+    out = {}
+    for name, s in _decay_variants(la, dev):
+        q, k, v = (t.clone().requires_grad_() for t in full[:3])
+        do = full[3]
+        o = la.lightning_attn2(q, k, v, s) if s is not None else la.lightning_attn2_no_decay(q, k, v)
+        o.backward(do)
+        ref = [o.detach()[:, :, sl], q.grad[:, :, sl], k.grad[:, :, sl], v.grad[:, :, sl]]
+        qs, ks, vs = (t[:, :, sl].contiguous().requires_grad_() for t in full[:3])
+        os_ = la_dist.lightning_attn_sp(qs, ks, vs, s)
+        os_.backward(do[:, :, sl].contiguous())
+        got = [os_.detach(), qs.grad, ks.grad, vs.grad]
+        errs = torch.tensor([_rel_l2(torch, a, b_) for a, b_ in zip(got, ref)], device=dev, dtype=torch.float64)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        out[name] = {k_: float(e_) for k_, e_ in zip(("o", "dq", "dk", "dv"), errs)}
+        del q, k, v, o, qs, ks, vs, os_
+    out["shard_tokens"] = Ls
+    out["reference"] = "single-GPU lightning_attn2 on the whole sequence, same seeded tensors on every rank"
+    return out
+
+
+def _window_reference(torch, q, k, v, do, s, kv_in, r_in, a0, W):
+    """fp32 torch restatement of one W-token window [a0, a0 + W) of a shard (lightning_attn2.py:73-84 forward,
+    :156-162 and :240-280, :335-395 backward), given the state entering the window from the left,
+        kv_in[h] = sum_{j < a0} lambda^(a0 - j) k_j^T v_j        (d, e),
+    and from the right,
+        r_in[h]  = sum_{j >= a0 + W} lambda^(j - a0 - W) q_j^T do_j   (d, e).
+    Returns o, dq, dk, dv of the window (intra-window terms + the two state terms)."""
+    qw, kw, vw, gw = (t[0, :, a0:a0 + W].float() for t in (q, k, v, do))  # (h, W, dim)
+    h = qw.shape[0]
+    dev = qw.device
+    sv = (torch.zeros(h, device=dev) if s is None else s.float().reshape(-1)[:h]).view(h, 1, 1)
+    r = torch.arange(W, device=dev, dtype=torch.float32)
+    diff = r[:, None] - r[None, :]
+    m = torch.where(diff >= 0, torch.exp(-sv * diff.clamp(min=0)), torch.zeros((), device=dev))  # (h, W, W): lambda^(r-c), c <= r
+    lam_r = torch.exp(-sv * r.view(1, W, 1))                # lambda^r
+    lam_end = torch.exp(-sv * (W - r).view(1, W, 1))        # lambda^(W - r)
+    p = (qw @ kw.transpose(1, 2)) * m
+    o = p @ vw + lam_r * (qw @ kv_in)
+    dp = (gw @ vw.transpose(1, 2)) * m
+    dq = dp @ kw + lam_r * (gw @ kv_in.transpose(1, 2))
+    dk = dp.transpose(1, 2) @ qw + lam_end * (vw @ r_in.transpose(1, 2))
+    dv = p.transpose(1, 2) @ gw + lam_end * (kw @ r_in)
+    return o, dq, dk, dv
+
+
+def _decayed_sum(torch, x, y, s, weights_from_end):
+    """sum_t w_t x_t^T y_t per head in fp32, w_t = lambda^(T - t) (weights_from_end) or lambda^t; x, y (1, h, T, dim)."""
+    xf, yf = x[0].float(), y[0].float()
+    h, T, _ = xf.shape
+    dev = xf.device
+    sv = (torch.zeros(h, device=dev) if s is None else s.float().reshape(-1)[:h]).view(h, 1, 1)
+    t = torch.arange(T, device=dev, dtype=torch.float32).view(1, T, 1)
+    w = torch.exp(-sv * ((T - t) if weights_from_end else t))
+    return (xf * w).transpose(1, 2) @ yf  # (h, dim_x, dim_y)
+
+
+def sp_parity_full(torch, dist, la, la_dist, dev, rank, world, q, k, v, do, Ls):
+    """Checks at the benchmark's shard length (Ls = 131072 tokens per GPU), per decay variant:
+    (a) rank 0: o and dq of its shard against the single-GPU op on the same 131072 tokens (they depend on earlier tokens
+        only, so they must agree; for ALiBi slopes also dk, dv on the tokens more than 32768 before the shard's end, where
+        the state arriving from later shards has decayed below fp32 resolution);
+    (b) last rank: o, dq of its first and last 256 tokens, and rank 0: dk, dv of its first and last 256 tokens, against an
+        fp32 torch restatement of the recurrence seeded with the incoming states, which are built independently of the
+        library from every rank's own fp32 sums (all-gathered).
+    Returns rel-L2 errors (max over the ranks that run each check)."""
+    W = 256
+    out = {}
+    for name, s in _decay_variants(la, dev):
+        qs, ks, vs = (t.detach().clone().requires_grad_() for t in (q, k, v))
+        o = la_dist.lightning_attn_sp(qs, ks, vs, s)
+        o.backward(do)
+        got = [o.detach(), qs.grad, ks.grad, vs.grad]
+        # independent fp32 shard sums: forward state contribution lambda^(L - j) k_j^T v_j, reverse lambda^t q_t^T do_t
+        f_loc = _decayed_sum(torch, k, v, s, True)
+        r_loc = _decayed_sum(torch, q, do, s, False)
+        f_all = torch.empty((world,) + tuple(f_loc.shape), device=dev)
+        r_all = torch.empty((world,) + tuple(r_loc.shape), device=dev)
+        dist.all_gather_into_tensor(f_all.view(-1, *f_loc.shape[1:]), f_loc.contiguous())
+        dist.all_gather_into_tensor(r_all.view(-1, *r_loc.shape[1:]), r_loc.contiguous())
+        sv = (torch.zeros(H, device=dev) if s is None else s.float().reshape(-1)[:H]).view(H, 1, 1)
+        lamL = torch.exp(-sv * float(Ls))
+        res = torch.zeros(8, device=dev, dtype=torch.float64)  # o, dq (vs single GPU), dk, dv (vs single GPU, prefix), 4 window checks
+        if rank == 0:
+            q1, k1, v1 = (t.detach().clone().requires_grad_() for t in (q, k, v))
+            o1 = la.lightning_attn2(q1, k1, v1, s) if s is not None else la.lightning_attn2_no_decay(q1, k1, v1)
+            o1.backward(do)
+            res[0] = _rel_l2(torch, got[0], o1.detach())
+            res[1] = _rel_l2(torch, got[1], q1.grad)
+            if name == "alibi":
+                cut = Ls - 32768
+                res[2] = _rel_l2(torch, got[2][:, :, :cut], k1.grad[:, :, :cut])
+                res[3] = _rel_l2(torch, got[3][:, :, :cut], v1.grad[:, :, :cut])
+            del q1, k1, v1, o1
+            # reverse-time state entering this shard's end from the later shards: sum_r lambda^((r-1) L) R_r
+            r_end = torch.zeros_like(r_loc)
+            for rr in range(world - 1, 0, -1):
+                r_end = lamL * r_end + r_all[rr]
+            zero_f = torch.zeros_like(f_loc)
+            for wi, a0 in enumerate((0, Ls - W)):
+                # state from the right of the window: local tokens after it + the later shards, decayed to the window's end
+                tail = _decayed_sum(torch, q[:, :, a0 + W:], do[:, :, a0 + W:], s, False) if a0 + W < Ls else torch.zeros_like(r_loc)
+                r_in = tail + torch.exp(-sv * float(Ls - a0 - W)) * r_end
+                kv_in = _decayed_sum(torch, k[:, :, :a0], v[:, :, :a0], s, True) if a0 > 0 else zero_f
+                _, _, rdk, rdv = _window_reference(torch, q, k, v, do, s, kv_in, r_in, a0, W)
+                res[4 + wi] = max(_rel_l2(torch, got[2][0, :, a0:a0 + W], rdk), _rel_l2(torch, got[3][0, :, a0:a0 + W], rdv))
+        if rank == world - 1:
+            kv_start = torch.zeros_like(f_loc)  # forward state entering this shard: sum_{r < rank} lambda^((rank-1-r) L) F_r
+            for rr in range(0, rank):
+                kv_start = lamL * kv_start + f_all[rr]
+            zero_r = torch.zeros_like(r_loc)
+            for wi, a0 in enumerate((0, Ls - W)):
+                head = _decayed_sum(torch, k[:, :, :a0], v[:, :, :a0], s, True) if a0 > 0 else torch.zeros_like(f_loc)
+                kv_in = head + torch.exp(-sv * float(a0)) * kv_start
+                tail = _decayed_sum(torch, q[:, :, a0 + W:], do[:, :, a0 + W:], s, False) if a0 + W < Ls else zero_r
+                ro, rdq, _, _ = _window_reference(torch, q, k, v, do, s, kv_in, tail, a0, W)
+                res[6 + wi] = max(_rel_l2(torch, got[0][0, :, a0:a0 + W], ro), _rel_l2(torch, got[1][0, :, a0:a0 + W], rdq))
+        dist.all_reduce(res, op=dist.ReduceOp.MAX)
+        keys = ("rank0_o_vs_single_gpu", "rank0_dq_vs_single_gpu", "rank0_dk_prefix_vs_single_gpu", "rank0_dv_prefix_vs_single_gpu",
+                "rank0_dk_dv_first_window_vs_fp32", "rank0_dk_dv_last_window_vs_fp32",
+                "last_rank_o_dq_first_window_vs_fp32", "last_rank_o_dq_last_window_vs_fp32")
+        out[name] = {k_: float(x) for k_, x in zip(keys, res) if not (name != "alibi" and "prefix" in k_)}
+        del qs, ks, vs, o, got
+    out["window_tokens"] = W
+    return out
+
+
+def leg_long_context(torch, dist, la, dev, rank, world, g, barrier):
+    """b=1, h=32, d=e=128, 131072 tokens per GPU (the sequence-parallel shard size of the 1M-token config).
+    N = 1: the plain single-GPU op at n = 131072. N > 1: sequence-parallel over N * 131072 tokens (two NCCL all-gathers of
+    2 MiB states per step), timed over 50 steps for ALiBi slopes and for slopes x 1e-3 (where the exchanged state matters
+    for every token), plus the untimed parity checks of sp_parity_small / sp_parity_full."""
+    from lightning_attention_b200 import distributed as la_dist
+
+    Ls = 131072
+    mk2 = lambda: (0.5 * torch.randn((1, H, Ls, D), device=dev, dtype=torch.float32, generator=g)).to(torch.bfloat16)
+    q2, k2, v2, do2 = mk2(), mk2(), mk2(), mk2()
+    q2.requires_grad_(); k2.requires_grad_(); v2.requires_grad_()
+    s_alibi = la._build_slope_tensor(H).to(dev)
+    timed = {}
+    for name, s in (("alibi", s_alibi), ("alibi_x1e-3", s_alibi * 1e-3)):
+        def sp_step():
+            q2.grad = k2.grad = v2.grad = None
+            o2 = la_dist.lightning_attn_sp(q2, k2, v2, s) if world > 1 else la.lightning_attn2(q2, k2, v2, s)
+            o2.backward(do2)
+
+        for _ in range(3):
+            sp_step()
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(50):
+            sp_step()
+        a1.record()
+        barrier()
+        tt = torch.tensor([a0.elapsed_time(a1) / 50], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        timed[name] = float(tt[0])
+    q2.grad = k2.grad = v2.grad = None
+    sp = {"mode": "sequence-parallel" if world > 1 else "single-gpu", "tokens_total": Ls * world, "steps_timed": 50,
+          "ms_per_step": timed["alibi"], "tokens_per_s": Ls * world / (timed["alibi"] * 1e-3),
+          "ms_per_step_slopes_x1e-3": timed["alibi_x1e-3"], "shape_per_gpu": [1, H, Ls, D]}
+    if world > 1:
+        try:
+            sp["parity"] = {"tolerance_rel_l2": 1e-2,
+                            "shard_8192_vs_single_gpu": sp_parity_small(torch, dist, la, la_dist, dev, rank, world),
+                            "shard_131072": sp_parity_full(torch, dist, la, la_dist, dev, rank, world, q2.detach(), k2.detach(),
+                                                           v2.detach(), do2, Ls)}
+            worst = 0.0
+            for grp in (sp["parity"]["shard_8192_vs_single_gpu"], sp["parity"]["shard_131072"]):
+                for val in grp.values():
+                    if isinstance(val, dict):
+                        worst = max([worst] + [x for x in val.values() if isinstance(x, float)])
+            sp["parity"]["worst_rel_l2"] = worst
+            sp["parity"]["pass"] = bool(worst <= 1e-2)
+        except Exception as ex:
+            sp["parity"] = {"error": repr(ex)[:300]}
+    return sp
+
+
+def cpu_reference_naive():
+    """The reference's own CPU path, timed on the host cores (rank 0, N = 1): `linear_attn` + autograd in fp32
+    (lightning_attn/ops/torch/linear_attention.py:27-34, through this package's pinned restatement of it, which builds the
+    same mask without the per-row Python loop) and `SimpleRMSNormTorch` (torch/srmsnorm.py:9-20). Sizes: BASELINE config 1,
+    and the sweep config (h=32, d=e=128) at n = 512, 1024, 2048 on ONE batch entry of the four (scaled x4 in tokens/s:
+    the batch entries are independent); n >= 8192 cannot run: the (h, n, n) fp32 mask and (b, h, n, n) scores are O(n^2)."""
+    import torch
+
+    from lightning_attention_b200.ops.torch import SimpleRMSNormTorch, linear_attn
+
+    torch.manual_seed(SEED)
+    out = {"cores": torch.get_num_threads(), "kind": "reference (naive O(n^2) torch path, fp32, CPU)", "attention": [], "srmsnorm": [],
+           "infeasible": "n >= 8192 infeasible: O(n^2) memory (mask h*n*n*4 B + scores b*h*n*n*4 B; 137 GB for the mask alone at n=32768)"}
+
+    def attn(b, h, n, d, tag, scale_b=1):
+        q, k, v = (torch.randn((b, h, n, d), dtype=torch.float32).requires_grad_() for _ in range(3))
+        s = torch.tensor([2.0 ** (-8.0 * (i + 1) / h) for i in range(h)]).reshape(h, 1, 1)
+        t0 = time.perf_counter()
+        o = linear_attn(q, k, v, s)
+        t1 = time.perf_counter()
+        o.sum().backward()
+        t2 = time.perf_counter()
+        out["attention"].append({"config": tag, "shape": [b, h, n, d, d], "fwd_s": t1 - t0, "bwd_s": t2 - t1,
+                                 "tokens_per_s": scale_b * b * n / (t2 - t0) / scale_b if scale_b == 1 else b * n / (t2 - t0),
+                                 "batch_entries_timed": b, "batch_entries_in_config": b * scale_b})
+
+    attn(1, 4, 256, 64, "config 1")
+    for n in (512, 1024, 2048):
+        attn(1, 32, n, 128, f"config 3, n={n}", scale_b=4)
+    for M, Nf in ((32768, 4096), (65536, 5120)):
+        x = torch.randn((M, Nf)).to(torch.bfloat16).requires_grad_()
+        dy = torch.randn((M, Nf)).to(torch.bfloat16)
+        norm = SimpleRMSNormTorch(Nf)
+        t0 = time.perf_counter()
+        y = norm(x)
+        t1 = time.perf_counter()
+        y.backward(dy)
+        t2 = time.perf_counter()
+        out["srmsnorm"].append({"shape": [M, Nf], "fwd_s": t1 - t0, "bwd_s": t2 - t1, "fwd_gbs": 4.0 * M * Nf / (t1 - t0) / 1e9,
+                                "bwd_gbs": 6.0 * M * Nf / (t2 - t1) / 1e9})
+    return out
+
+
 def main():
     global N_TOK
     # Libraries (NCCL's version banner, for one) print to file descriptor 1; the contract is ONE JSON line on stdout.
@@ -325,6 +802,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="only the headline step and its roofline (profiling runs: few launches before the captured ones)")
     ap.add_argument("--n", type=int, default=N_TOK, help="sequence length (default: the benchmark's largest point)")
     ap.add_argument("--trace", action="store_true",
                     help="print the in-kernel clock trace of the attention block kernel (one JSON line per direction) and exit")
@@ -349,6 +828,10 @@ def main():
         run_trace(emit)
         return
 
+    # pinned host buffers of the end-to-end leg should be local to the GPU's NUMA node: set the affinity before torch
+    # starts its threads and before anything is allocated
+    numa = numa_pin(local_rank) if not args.no_e2e else {"numa_node": None}
+
     import torch
     import torch.distributed as dist
 
@@ -362,11 +845,20 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L = _lib.lib()
+    full = (args.n == 32768) and not args.headline_only
+    hbm_peak, tf_peak, peak_kind = load_peaks()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def guarded(fn, *a, **kw):
+        try:
+            return fn(*a, **kw)
+        except Exception as ex:
+            torch.cuda.synchronize()
+            return {"error": repr(ex)[:300]}
 
     # ---- synthetic inputs, resident in HBM (4 x 1.07 GB, far larger than the 126 MB L2) ----------------
     g = torch.Generator(device=dev)
@@ -404,6 +896,7 @@ def main():
     barrier()
     launches = L.lab200_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
+    del o
     total_ms = ev[0][0].elapsed_time(end)
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
@@ -414,56 +907,28 @@ def main():
     ms_per_step = total_ms / args.steps
     tokens_per_step = B * N_TOK * world
     value = tokens_per_step / (ms_per_step * 1e-3)
+    # the status word the bounded waits of the block kernels write on expiry: surfaced by the library one call late
+    device_status = int(L.lab200_last_status())
 
-    # ---- SRMSNorm fwd+bwd GB/s on (32768, 4096) bf16 (rank 0) -------------------------------------------
-    srms = None
-    if rank == 0:
-        M, Nf = 4 * 8192, 4096
-        x = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g).requires_grad_()
-        dy = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g)
-        norm = la.SimpleRMSNorm(Nf)
-        # 1 GiB: flushes L2 and keeps the GPU busy long enough for the host to enqueue forward and backward behind it,
-        # so the events bracket device time, not the autograd engine's launch latency
-        flush = torch.empty(1024 * 1024 * 1024, dtype=torch.uint8, device=dev)
-        tf, tb = [], []
-        for i in range(8):
-            x.grad = None
-            flush.zero_()
-            a, b_, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-            a.record(); y = norm(x); b_.record(); y.backward(dy); c.record()
-            torch.cuda.synchronize()
-            if i >= 3:
-                tf.append(a.elapsed_time(b_)); tb.append(b_.elapsed_time(c))
-        fms, bms = statistics.median(tf), statistics.median(tb)
-        srms = {"shape": [M, Nf], "fwd_ms": fms, "bwd_ms": bms, "fwd_gbs": 4.0 * M * Nf / fms / 1e6,
-                "bwd_gbs": 6.0 * M * Nf / bms / 1e6, "note": "public API (autograd Function); L2 flushed between reps by a 1 GiB memset the launches queue behind"}
-        # the same rows through the fused norm + sigmoid gate (6 and 10 bytes per element)
-        try:
-            gate = torch.randn((M, Nf), device=dev, dtype=torch.bfloat16, generator=g).requires_grad_()
-            tf, tb = [], []
-            for i in range(8):
-                x.grad = gate.grad = None
-                flush.zero_()
-                a, b_, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-                a.record(); y = la.srmsnorm_sigmoid_gate(x, gate); b_.record(); y.backward(dy); c.record()
-                torch.cuda.synchronize()
-                if i >= 3:
-                    tf.append(a.elapsed_time(b_)); tb.append(b_.elapsed_time(c))
-            gf, gb = statistics.median(tf), statistics.median(tb)
-            srms.update({"gate_fwd_ms": gf, "gate_bwd_ms": gb, "gate_fwd_gbs": 6.0 * M * Nf / gf / 1e6,
-                         "gate_bwd_gbs": 10.0 * M * Nf / gb / 1e6})
-            del gate
-        except Exception as ex:
-            srms["gate_error"] = repr(ex)[:200]
-        del x, dy, flush
+    # ---- single-GPU time of the whole step on this rank (T_1 of the fixed-total-work split below) -------------
+    t1_local = fwd_ms + bwd_ms
+
+    # ---- legs on rank 0 only -------------------------------------------------------------------------------------
+    srms = srms2 = proj = decode = config2 = sweep = sustained = None
+    if rank == 0 and full:
+        srms = guarded(leg_srmsnorm, torch, la, L, dev, g, 4 * 8192, 4096, True)
+        srms2 = guarded(leg_srmsnorm, torch, la, L, dev, g, 2 * 32768, 5120, False)
+        config2 = guarded(leg_config2, torch, la, dev, hbm_peak)
+        sweep = guarded(leg_sweep, torch, la, dev, s)
+        if world == 1:
+            sustained = guarded(leg_sustained, torch, step, 2.0, local_rank)
 
     # ---- projection layout: q, k, v, do as (b, h, n, d) views of (b, n, h, d) tensors, as a caller's projections give them.
     # "in_place": the op reads and writes that layout directly. "with_copies": what the reference's wrapper does with such
     # views - .contiguous() on q, k, v and do, and a rearranging copy of o and of the three gradients on the way back.
-    proj = None
-    if rank == 0:
+    if rank == 0 and full:
         try:
-            xq, xk, xv = (t.detach().transpose(1, 2).contiguous().requires_grad_() for t in (q, k, v))
+            xq, xk, xv = (t_.detach().transpose(1, 2).contiguous().requires_grad_() for t_ in (q, k, v))
             xdo = do.transpose(1, 2).contiguous()
 
             def in_place():
@@ -477,18 +942,7 @@ def main():
                                         xv.transpose(1, 2).contiguous(), s)
                 o_.transpose(1, 2).contiguous().backward(xdo)
 
-            res = {}
-            for name, fn in (("in_place", in_place), ("with_copies", with_copies)):
-                for _ in range(2):
-                    fn()
-                p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                p0.record()
-                for _ in range(5):
-                    fn()
-                p1.record()
-                torch.cuda.synchronize()
-                res[name + "_ms"] = p0.elapsed_time(p1) / 5
+            res = {name + "_ms": event_time(torch, fn, 5, warm=2) for name, fn in (("in_place", in_place), ("with_copies", with_copies))}
             proj = {"shape_b_n_h_d": [B, N_TOK, H, D], **res,
                     "note": "fwd+bwd with q, k, v, do given as (b, n, h, d) tensors; tnl_attn.py:56-64 style caller"}
             del xq, xk, xv, xdo
@@ -496,71 +950,43 @@ def main():
             proj = {"error": repr(ex)[:200]}
 
     # ---- decode step (inference API): 256 sequences x 32 heads, d=e=128; the fp32 states (537 MB) exceed L2 -----
-    decode = None
-    if rank == 0:
+    if rank == 0 and full:
         try:
             bd = 256
             st = torch.zeros((bd, H, D, D), device=dev, dtype=torch.float32)
             qd, kd, vd = (torch.randn((bd, H, D), device=dev, generator=g).to(torch.bfloat16) for _ in range(3))
-            for _ in range(3):
-                la.lightning_attn_decode(qd, kd, vd, s, st)
-            d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            d0.record()
-            for _ in range(20):
-                la.lightning_attn_decode(qd, kd, vd, s, st)
-            d1.record()
-            torch.cuda.synchronize()
-            dms = d0.elapsed_time(d1) / 20
+            dms = event_time(torch, lambda: la.lightning_attn_decode(qd, kd, vd, s, st), 20)
             decode = {"shape": [bd, H, D, D], "ms_per_step": dms, "gbs": 8.0 * st.numel() / dms / 1e6,
                       "tokens_per_s": bd / (dms * 1e-3), "note": "one token per sequence; bytes = fp32 state read + written"}
             del st, qd, kd, vd
         except Exception as ex:
             decode = {"error": repr(ex)[:200]}
 
-    # ---- long-context leg: b=1, h=32, d=e=128, 131072 tokens per GPU (the sequence-parallel shard size) ----
-    # N = 1: plain single-GPU op at n = 131072. N > 1: sequence-parallel over N*131072 tokens (two NCCL
-    # all-gathers of 2 MiB states per step). Same per-GPU work in both, so the ratio of the two times is the
-    # sequence-parallel overhead.
-    sp = None
-    if args.n == 32768:
-        try:
-            from lightning_attention_b200 import distributed as la_dist
+    # ---- batch x heads sharding at fixed total work (all ranks) ---------------------------------------------------
+    bh_strong = None
+    if full:
+        tt = torch.tensor([t1_local], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.broadcast(tt, src=0)  # T_1 as rank 0 measured it on the whole problem
+        if world > 1:
+            # every rank needs the SAME full tensors to slice: regenerate them from rank 0's seed
+            g0 = torch.Generator(device=dev)
+            g0.manual_seed(SEED)
+            mk0 = lambda: torch.randn((B, H, N_TOK, D), device=dev, dtype=torch.float32, generator=g0).to(torch.bfloat16)
+            fq, fk, fv, fdo = mk0(), mk0(), mk0(), mk0()
+        else:
+            fq, fk, fv, fdo = q, k, v, do
+        bh_strong = guarded(leg_bh_strong, torch, dist, la, dev, rank, world, fq, fk, fv, fdo, s, float(tt[0]))
+        del fq, fk, fv, fdo
 
-            Ls = 131072
-            mk2 = lambda: (0.5 * torch.randn((1, H, Ls, D), device=dev, dtype=torch.float32, generator=g)).to(torch.bfloat16)
-            q2, k2, v2, do2 = mk2(), mk2(), mk2(), mk2()
-            q2.requires_grad_(); k2.requires_grad_(); v2.requires_grad_()
-
-            def sp_step():
-                q2.grad = k2.grad = v2.grad = None
-                o2 = la_dist.lightning_attn_sp(q2, k2, v2, s) if world > 1 else la.lightning_attn2(q2, k2, v2, s)
-                o2.backward(do2)
-
-            for _ in range(3):
-                sp_step()
-            barrier()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for _ in range(5):
-                sp_step()
-            a1.record()
-            barrier()
-            tt = torch.tensor([a0.elapsed_time(a1) / 5], device=dev, dtype=torch.float64)
-            if world > 1:
-                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            sp = {"mode": "sequence-parallel" if world > 1 else "single-gpu", "tokens_total": Ls * world,
-                  "ms_per_step": float(tt[0]), "tokens_per_s": Ls * world / (float(tt[0]) * 1e-3),
-                  "shape_per_gpu": [1, H, Ls, D]}
-            del q2, k2, v2, do2
-        except Exception as ex:
-            sp = {"error": repr(ex)[:200]}
+    # ---- long-context leg (all ranks) --------------------------------------------------------------------------------
+    sp = guarded(leg_long_context, torch, dist, la, dev, rank, world, g, barrier) if full else None
 
     # ---- end to end through the public API with pinned host buffers ---------------------------------------
     e2e = None
     nbytes = q.numel() * 2
     try:
-        if args.no_e2e:
+        if args.no_e2e or args.headline_only:
             raise RuntimeError("skipped by --no-e2e")
         hq, hk, hv, hdo = (torch.empty((B, H, N_TOK, D), dtype=torch.bfloat16, pin_memory=True) for _ in range(4))
         ho, hdq, hdk, hdv = (torch.empty((B, H, N_TOK, D), dtype=torch.bfloat16, pin_memory=True) for _ in range(4))
@@ -574,12 +1000,12 @@ def main():
         gh = 4
         groups = [(ib, h0, h0 + gh) for ib in range(B) for h0 in range(0, H, gh)]
         s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-        main = torch.cuda.current_stream(dev)
+        main_stream = torch.cuda.current_stream(dev)
 
         def e2e_step():
             ev_in = [torch.cuda.Event() for _ in groups]
             ev_done = [torch.cuda.Event() for _ in groups]
-            s_in.wait_stream(main)
+            s_in.wait_stream(main_stream)
             with torch.cuda.stream(s_in):
                 for gi, (ib, h0, h1) in enumerate(groups):
                     for dst, src in ((dq_, hq), (dk_, hk), (dv_, hv), (ddo_, hdo)):
@@ -587,19 +1013,19 @@ def main():
                     ev_in[gi].record(s_in)
             outs = []
             for gi, (ib, h0, h1) in enumerate(groups):
-                main.wait_event(ev_in[gi])
-                qq, kk, vv = (t[ib:ib + 1, h0:h1].detach().requires_grad_() for t in (dq_, dk_, dv_))
+                main_stream.wait_event(ev_in[gi])
+                qq, kk, vv = (t_[ib:ib + 1, h0:h1].detach().requires_grad_() for t_ in (dq_, dk_, dv_))
                 oo = la.lightning_attn2(qq, kk, vv, s[h0:h1])
                 oo.backward(ddo_[ib:ib + 1, h0:h1])
                 outs.append((oo.detach(), qq.grad, kk.grad, vv.grad))
-                ev_done[gi].record(main)
+                ev_done[gi].record(main_stream)
             with torch.cuda.stream(s_out):
                 for gi, (ib, h0, h1) in enumerate(groups):
                     s_out.wait_event(ev_done[gi])
                     for dst, src in zip((ho, hdq, hdk, hdv), outs[gi]):
                         dst[ib, h0:h1].copy_(src[0], non_blocking=True)
                         src.record_stream(s_out)
-            main.wait_stream(s_out)
+            main_stream.wait_stream(s_out)
 
         e2e_step()
         barrier()
@@ -615,28 +1041,39 @@ def main():
         e2e_ms = float(t[0]) / args.e2e_steps
         e2e = {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes,
-               "note": "q,k,v,do copied from pinned host memory and o,dq,dk,dv copied back every step, per rank; 32 groups of 4 (batch, head) pairs pipelined over copy-in / compute / copy-out streams"}
+               "host_gbs_all_ranks": 8.0 * nbytes * world / (e2e_ms * 1e-3) / 1e9, "numa": numa,
+               "note": "q,k,v,do copied from pinned host memory and o,dq,dk,dv copied back every step, per rank; 32 groups of 4 "
+                       "(batch, head) pairs pipelined over copy-in / compute / copy-out streams; pinned buffers allocated with "
+                       "the process bound to the CPUs of its GPU's NUMA node"}
+        del hq, hk, hv, hdo, ho, hdq, hdk, hdv
     except Exception as ex:  # pinned allocation can fail on a small host
         e2e = {"value": None, "unit": "tokens/s", "error": repr(ex)[:200]}
 
     if rank == 0:
-        hbm_peak, tf_peak, peak_kind = load_peaks()
         units = B * H * N_TOK
         launch_ms = (fwd_ms + bwd_ms) / LA_LAUNCHES_PER_STEP
         achieved = ALG_BYTES_PER_UNIT * units / LA_LAUNCHES_PER_STEP / (launch_ms * 1e-3) / 1e9
+        moved = PASSES_MOVED_PER_STEP * units * D * 2  # bytes the three launches read and write
         roofline = {
-            "bound": "hbm", "kernel": "la_pipe_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-            "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-            "launch_ms": launch_ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "bound": "hbm", "kernel": "la_pipe_kernel (o, dq) + la_dkdv2_kernel (dk, dv)", "achieved": achieved, "peak": hbm_peak,
+            "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
+            "traffic": PASSES_MOVED_PER_STEP * NCU_BYTES_PER_PASS_N8192 * (N_TOK / 8192.0) / LA_LAUNCHES_PER_STEP,
+            "launches_per_step": LA_LAUNCHES_PER_STEP, "launch_ms": launch_ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "fwd_frac": 1024.0 * units / (fwd_ms * 1e-3) / 1e9 / hbm_peak, "bwd_frac": 1792.0 * units / (bwd_ms * 1e-3) / 1e9 / hbm_peak,
+            "moved_gbs": moved / ((fwd_ms + bwd_ms) * 1e-3) / 1e9,
             "alg_tflops": ALG_FLOP_PER_UNIT * units / ((fwd_ms + bwd_ms) * 1e-3) / 1e12,
             "frac_tensor": ALG_FLOP_PER_UNIT * units / ((fwd_ms + bwd_ms) * 1e-3) / 1e12 / tf_peak,
+            "note": "achieved = algorithmic bytes of a step (2816 B per (token, head)) / launches per step / mean launch time; "
+                    "traffic = DRAM bytes per launch scaled from the ncu capture at n = 8192 (linear in n); moved_gbs = bytes the "
+                    "launches actually read and write (14 tensor passes against 11 compulsory) over the step time",
         }
-        cpu = None
-        if world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_ref = None
+        if world == 1 and not args.no_cpu_baseline and not args.headline_only:
             pairs = 2 * host_threads()
             dt, tps = cpu_sample(pairs)
             cpu = {"value": tps, "unit": "tokens/s", "cores": host_threads(), "kind": "port", "seconds": dt,
                    "sample": f"{pairs} of {B * H} (batch, head) pairs at n={N_TOK}, fp32 numpy block recurrences, fwd+bwd, one pair per host thread, scaled to the full step"}
+            cpu_ref = guarded(cpu_reference_naive)
         out = {
             "metric": "lightning2_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -649,7 +1086,9 @@ def main():
                                      "step_time_ratio": (REF_LIGHTNING2_FWD[N_TOK] + REF_LIGHTNING2_BWD[N_TOK]) / ms_per_step}
                                     if N_TOK in REF_LIGHTNING2_FWD else None),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "srmsnorm": srms, "long_context": sp, "decode": decode, "projection_layout": proj,
+            "device_status": device_status, "sustained": sustained,
+            "srmsnorm": srms, "srmsnorm_5120": srms2, "config2": config2, "sweep": sweep, "bh_strong": bh_strong,
+            "long_context": sp, "decode": decode, "projection_layout": proj, "cpu_baseline_reference": cpu_ref,
         }
         emit(json.dumps(out))
     if world > 1:

@@ -4,7 +4,8 @@
  *
  * Conventions
  *  - Every pointer is a CUDA device pointer owned by the caller unless stated otherwise; the
- *    library never allocates or frees device memory.
+ *    library never allocates or frees device memory (its only allocation is 256 bytes of pinned host
+ *    memory per device for lab200_last_status).
  *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and the calls return
  *    without synchronising (except lab200_read_status).
  *  - Return value 0 means the work was enqueued; any other value is an error code
@@ -31,7 +32,7 @@ extern "C" {
 #define LAB200_F16 1
 #define LAB200_BF16 2
 /* Layout flag, OR-ed into the dtype argument of the attention entry points (lab200_la_generic*, lab200_la2_fwd*,
- * lab200_la2_bwd): every 16-bit tensor of the call is (b, n, h, dim) contiguous - what the projection GEMMs around the
+ * lab200_la2_bwd, lab200_la2_dkdv): every 16-bit tensor of the call is (b, n, h, dim) contiguous - what the projection GEMMs around the
  * op produce and consume (examples/module/tnl_attn.py:56-64 rearranges to (b, h, n, d) and back) - instead of
  * (b, h, n, dim). States stay (bh, dv, dk). Needs bh = b * h with whole batches and dk <= 128. */
 #define LAB200_LAYOUT_BNHD 0x100
@@ -175,22 +176,61 @@ int lab200_la2_fwd_static(const void* q, const void* k, const void* v, const flo
                           int b, int h, int n, int d, int e, int chunks, int dtype, void* stream);
 
 /* dq, dk, dv = LightningAttention2.backward(do): lightning_attn2.py:437-504 and
- * lightning_attn2_no_decay.py:403-468. Workspace size: lab200_la_workspace_bytes(b*h, n, max(d,e), max(d,e), chunks). */
+ * lightning_attn2_no_decay.py:403-468. dq is one forward-time launch of the generic product, dk and dv come out of one
+ * fused reverse-time sweep (d, e <= 128; two generic launches otherwise).
+ * Workspace size: lab200_la2_bwd_workspace_bytes(b, h, n, d, e, chunks). */
 int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slopes, const void* dout,
                    void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h,
                    int n, int d, int e, int chunks, int dtype, void* stream);
 
-/* dk and dv of the same backward pass in ONE reverse-time sweep that reads q, k, v, do once (6 tensor passes instead
- * of the 8 that two generic launches move); one CTA per (batch, head) pair, d, e <= 128. Same results as the dk, dv of
- * lab200_la2_bwd. Stands in for the dk/dv halves of _bwd_intra_kernel (lightning_attn2.py:156-162) and of the
- * reverse sweep of _bwd_inter_kernel (:335-395). Workspace: 256 bytes (status word only). */
+/* Bytes of workspace lab200_la2_bwd needs: the largest need of the three products it runs ((dk, dv) = (e, d) for dq
+ * and for dk/dv, (d, e) for dv on the unfused path), each with its own chunk plan when `chunks` = 0. */
+size_t lab200_la2_bwd_workspace_bytes(int b, int h, int n, int d, int e, int chunks);
+
+/*
+ * dk and dv of the same backward pass in ONE reverse-time sweep that reads q, k, v, do once and writes dk, dv (6 tensor
+ * passes instead of the 8 that two generic launches move); d, e <= 128. Same results as the dk, dv of lab200_la2_bwd.
+ * Stands in for the dk/dv halves of _bwd_intra_kernel (lightning_attn2.py:156-162) and for the reverse sweep of
+ * _bwd_inter_kernel (:335-395).
+ * state_in: optional (b*h, d, e) fp32 reverse-time state sum_t lambda^t q_t^T do_t entering the sequence from tokens
+ * after its end (sequence parallelism; needs n % 128 == 0), or NULL.
+ * chunks: 0 = automatic, otherwise the number of sequence chunks processed by independent CTAs; with more than one chunk
+ * the call first computes the state entering every chunk (a state-only pass over do and q and a scan).
+ * resume != 0: `workspace` already holds those per-chunk states from lab200_la_generic(NULL, do, q, ..., dk = e, dv = d,
+ * reverse = 1, state_only = 1, same chunks) with a zero initial state; the decayed `state_in` is added and the state-only
+ * pass is skipped (the two-step protocol of lab200_la_generic_resume).
+ * Workspace: lab200_la_workspace_bytes(b*h, n, e, d, chunks).
+ */
 int lab200_la2_dkdv(const void* q, const void* k, const void* v, const float* slopes, const void* dout,
-                    void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h, int n,
-                    int d, int e, int dtype, void* stream);
+                    void* dk, void* dv, const float* state_in, void* workspace, size_t workspace_bytes, int b,
+                    int h, int n, int d, int e, int chunks, int resume, int dtype, void* stream);
 
 /* Synchronises `stream` and returns the device-side status word of the last attention call that
  * used `workspace` (0, or one of LAB200_ERR_WAIT_*). Negative: the copy itself failed. */
 int lab200_read_status(const void* workspace, void* stream);
+
+/*
+ * Status without a host synchronisation. After the last launch of every attention call that takes a workspace the
+ * library enqueues a 4-byte copy of the call's status word into a ring (64 slots per device) of pinned host memory,
+ * which it allocates with cudaHostAlloc on the first such call on a device (make that call outside stream capture).
+ * lab200_last_status() looks through the ring of the current device and returns - and clears - the first non-zero word
+ * (a LAB200_ERR_WAIT_* code: a bounded wait of an EARLIER call ran out and that call's outputs are invalid), or 0.
+ * It never blocks; the report is at least one call late (the copy runs behind the kernels) and a word that is not
+ * collected within 64 later calls is overwritten. The Python operators call it before every launch and raise.
+ * No counterpart in the reference (its kernels have no waits that can run out).
+ */
+int lab200_last_status(void);
+
+/* lab200_read_status for the scratch array built into the library (lab200_la2_fwd_static has no workspace argument
+ * to read it from): synchronises `stream` and returns the status word of the last static call on the current device.
+ * Allocates nothing. */
+int lab200_static_status(void* stream);
+
+/* Test hook for the error path: one tiny kernel waits - with the bounded wait of the block kernels and a budget of
+ * `budget_cycles` SM clocks (at most 1e8) - on a barrier nothing arrives on, so the wait runs out and the kernel writes
+ * LAB200_ERR_WAIT_INPUT into the workspace's status word and returns; the call then posts the word like every attention
+ * call does. No copy, tensor memory or MMA is in flight in that kernel. No counterpart in the reference. */
+int lab200_debug_wait_expiry(void* workspace, size_t workspace_bytes, long long budget_cycles, void* stream);
 
 /* y = x * rsqrt(mean(x^2, last dim) + eps), rstd saved per row: _SrmsNorm.forward /
  * srms_norm_fw, srmsnorm.py:12-33, 78-122. x, y: (M, N); rstd: (M) fp32. N * sizeof(elem) <= 65536. */

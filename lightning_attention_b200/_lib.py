@@ -56,9 +56,17 @@ def lib():
         L.lab200_la2_fwd_static.restype = i
         L.lab200_la2_fwd_static.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, vp]
         L.lab200_la2_dkdv.restype = i
-        L.lab200_la2_dkdv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, vp]
+        L.lab200_la2_dkdv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, i, vp]
+        L.lab200_la2_bwd_workspace_bytes.restype = sz
+        L.lab200_la2_bwd_workspace_bytes.argtypes = [i, i, i, i, i, i]
         L.lab200_la2_bwd.restype = i
         L.lab200_la2_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i, i, i, i, i, i, i, vp]
+        L.lab200_last_status.restype = i
+        L.lab200_last_status.argtypes = []
+        L.lab200_static_status.restype = i
+        L.lab200_static_status.argtypes = [vp]
+        L.lab200_debug_wait_expiry.restype = i
+        L.lab200_debug_wait_expiry.argtypes = [vp, sz, ll, vp]
         L.lab200_read_status.restype = i
         L.lab200_read_status.argtypes = [vp, vp]
         L.lab200_srmsnorm_fwd.restype = i
@@ -71,7 +79,7 @@ def lib():
 
 EXPORTS = [
     "lab200_version", "lab200_launch_count", "lab200_la_debug_trace", "lab200_error_string", "lab200_la_plan_chunks", "lab200_la_workspace_bytes",
-    "lab200_la_generic", "lab200_la_generic_resume", "lab200_la_generic_resume_swapped", "lab200_la_combine_states", "lab200_la_decode_step", "lab200_la2_fwd", "lab200_la2_fwd_static", "lab200_la2_bwd", "lab200_la2_dkdv", "lab200_read_status",
+    "lab200_la_generic", "lab200_la_generic_resume", "lab200_la_generic_resume_swapped", "lab200_la_combine_states", "lab200_la_decode_step", "lab200_la2_fwd", "lab200_la2_fwd_static", "lab200_la2_bwd", "lab200_la2_bwd_workspace_bytes", "lab200_la2_dkdv", "lab200_read_status", "lab200_last_status", "lab200_static_status", "lab200_debug_wait_expiry",
     "lab200_srmsnorm_fwd", "lab200_srmsnorm_bwd", "lab200_srmsnorm_gate_fwd", "lab200_srmsnorm_gate_bwd",
 ]
 
@@ -87,6 +95,18 @@ def check(rc, what):
     if rc != 0:
         msg = lib().lab200_error_string(rc).decode()
         raise RuntimeError(f"{what} failed with code {rc}: {msg}")
+
+
+def raise_on_device_status(device):
+    """Raises if a bounded wait of an earlier attention call on `device` ran out (lab200_last_status): the kernels then
+    return early with an error word instead of hanging, and the outputs of that call are invalid. Non-blocking; called by
+    the operators before they enqueue new work, so the report comes one call late."""
+    with torch.cuda.device(device):
+        rc = lib().lab200_last_status()
+    if rc != 0:
+        msg = lib().lab200_error_string(rc).decode()
+        raise RuntimeError(f"an earlier lightning attention call on {device} failed on the device with code {rc} ({msg}); "
+                           "its outputs are invalid")
 
 
 def ptr(t):

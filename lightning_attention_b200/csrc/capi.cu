@@ -12,7 +12,7 @@
 #include "../../include/lightning_b200.h"
 #include "la_kernels.cuh"
 #include "la_pipe_kernel.cuh"
-#include "la_dkdv_kernel.cuh"
+#include "la_dkdv2_kernel.cuh"
 #include "srmsnorm_kernels.cuh"
 
 using namespace lab200;
@@ -219,7 +219,9 @@ int la_validate(const void* a, const void* bm, const void* c, const void* out, c
                 int dtype);
 
 // The generic product without the status reset (so that composite calls share one status word).
-enum : int { RESUME = 1, RESUME_SWAPPED = 2, RESUME_NO_REBASE = 4 };
+// PREFIX_ONLY: stop once the state entering every chunk is in the workspace (computed, or with RESUME taken over from
+// an earlier call and rebased); the block loop is the caller's business (the fused dk+dv sweep). a and out may be null.
+enum : int { RESUME = 1, RESUME_SWAPPED = 2, RESUME_NO_REBASE = 4, PREFIX_ONLY = 8 };
 
 // Number of chunks la_generic_impl cuts the sequence into.
 int chunk_count(int bh, int n, int dk, int dv, int chunks) {
@@ -234,7 +236,8 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
                     const float* state_in, float* state_out, void* workspace, size_t workspace_bytes, int bh, int h,
                     int n, int dk, int dv, int reverse, int state_only, int chunks, int dtype, cudaStream_t st,
                     int resume = 0) {
-  int rc = la_validate(a, bm, c, out, state_in, state_out, workspace, bh, h, n, dk, dv, state_only, dtype);
+  const bool prefix_only = (resume & PREFIX_ONLY) != 0;
+  int rc = la_validate(a, bm, c, out, state_in, state_out, workspace, bh, h, n, dk, dv, prefix_only ? 2 : state_only, dtype);
   if (rc != LAB200_OK) return rc;
   const int layout = (dtype & LAB200_LAYOUT_BNHD) ? 1 : 0;
   dtype &= 0xff;
@@ -250,7 +253,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   CUtensorMap tA, tB, tC, tO;
   if ((rc = make_tmap(&tB, bm, bh, n, dk, dtype, layout, h)) != LAB200_OK) return rc;
   if ((rc = make_tmap(&tC, c, bh, n, dv, dtype, layout, h)) != LAB200_OK) return rc;
-  if (state_only) {
+  if (state_only || prefix_only) {
     tA = tB;
     tO = tC;
   } else {
@@ -273,6 +276,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   p.trace_blocks = g_trace_blocks.load(std::memory_order_relaxed);
 
   if (nchunks == 1) {
+    if (prefix_only) return LAB200_OK;  // a single sweep takes state_in as it is
     p.chunk0 = 0;
     p.state_slots = 1;
     p.state_in = state_in;
@@ -282,7 +286,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
 
   // three phases: local chunk states -> decayed scan -> block loop per chunk with its incoming state
   float* states = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + WS_HEADER);
-  if (resume) {
+  if (resume & RESUME) {
     // the workspace already holds the per-chunk prefix states of a preceding call: go straight to the block loop.
     // RESUME_SWAPPED: they belong to the product with Bm and C exchanged, i.e. they are the transposes (dk == dv).
     // Unless RESUME_NO_REBASE is set they were computed from a zero initial state and the decayed incoming state is added.
@@ -301,6 +305,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
       g_launches.fetch_add(1, std::memory_order_relaxed);
       if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
     }
+    if (prefix_only) return LAB200_OK;
     p.state_slots = nchunks;
     p.chunk0 = 0;
     p.state_in = states;
@@ -323,7 +328,7 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
                                              p.reverse, skip_last, total);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
-  if (state_only) return LAB200_OK;
+  if (state_only || prefix_only) return LAB200_OK;
 
   p.chunk0 = 0;
   p.state_in = states;
@@ -333,62 +338,68 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
 
 // ---- fused dk + dv (one reverse sweep) -----------------------------------------------------------------
 int smem_bytes_dkdv(int ne) {
-  return 12 * LA_SLAB_BYTES + ne * LA_SLAB_BYTES + 2 * LDK_NUM_BARS * 8 + 16 + 512 + 1024;
+  return 12 * LA_SLAB_BYTES + ne * LA_SLAB_BYTES + 2 * LD2_NUM_BARS * 8 + 16 + 512 + 1024;
 }
 
 template <int ND, int NE, int FMT>
-int launch_dkdv_one(const CUtensorMap (&tm)[6], const LaDkdvParams& p, dim3 grid, int smem, cudaStream_t st) {
-  auto kern = la_dkdv_kernel<ND, NE, FMT>;
+int launch_dkdv_one(const CUtensorMap (&tm)[4], const LaDkdvParams& p, dim3 grid, int smem, cudaStream_t st) {
+  auto kern = la_dkdv2_kernel<ND, NE, FMT>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     cudaGetLastError();
     return LAB200_ERR_CUDA;
   }
-  kern<<<grid, LAP_THREADS, smem, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], p);
+  kern<<<grid, LAP_THREADS, smem, st>>>(tm[0], tm[1], tm[2], tm[3], p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
 }
 
-// The fused dk+dv sweep moves 6 instead of 8 tensor passes but its two mask passes per block sit on one dependency
-// chain, which today makes it a few percent slower than two generic launches; lab200_la2_bwd therefore uses it only
-// when LIGHTNING_B200_FUSED_BWD=1 is set. lab200_la2_dkdv always uses it.
+// lab200_la2_bwd computes dk and dv with the fused sweep (6 tensor passes instead of the 8 of two generic launches)
+// unless LIGHTNING_B200_FUSED_BWD=0 is set (A/B comparisons). lab200_la2_dkdv always uses it.
 bool use_fused_dkdv() {
   static const bool on = [] {
     const char* e = getenv("LIGHTNING_B200_FUSED_BWD");
-    return e && e[0] == '1';
+    return !(e && e[0] == '0');
   }();
   return on && use_pipelined_kernel();
 }
 
-// dk and dv in one launch; only the unchunked case (one CTA per (batch, head) pair). Returns LAB200_ERR_SHAPE if the
-// shape is not covered, in which case the caller falls back to two generic launches.
+bool dkdv_shape_ok(int d, int e) { return d <= 128 && e <= 128 && (d % 16) == 0 && (e % 16) == 0 && d >= 16 && e >= 16; }
+
+// dk and dv in one launch per chunk of the sequence. `states`: nullptr (one chunk: the sweep starts from a zero state) or
+// the reverse-time state entering every chunk, [bh][nchunks][d][e] fp32. Returns LAB200_ERR_SHAPE if the shape is not
+// covered, in which case the caller falls back to two generic launches.
 int la_dkdv_impl(const void* q, const void* k, const void* v, const void* dout, const float* slopes, void* dk, void* dv,
-                 void* workspace, int bh, int h, int n, int d, int e, int dtype, cudaStream_t st) {
-  if (d > 128 || e > 128 || (d % 16) || (e % 16) || d < 16 || e < 16) return LAB200_ERR_SHAPE;
+                 void* workspace, const float* states, int nchunks, int bpc, int bh, int h, int n, int d, int e, int dtype,
+                 cudaStream_t st) {
+  const int layout = (dtype & LAB200_LAYOUT_BNHD) ? 1 : 0;
+  dtype &= 0xff;
+  if (!dkdv_shape_ok(d, e)) return LAB200_ERR_SHAPE;
   const int nd = (d + 63) / 64, ne = (e + 63) / 64;
   const int smem = smem_bytes_dkdv(ne);
   if (smem > SMEM_LIMIT) return LAB200_ERR_SHAPE;
-  CUtensorMap tm[6];
+  CUtensorMap tm[4];
   int rc;
-  if ((rc = make_tmap(&tm[0], q, bh, n, d, dtype)) != LAB200_OK) return rc;
-  if ((rc = make_tmap(&tm[1], k, bh, n, d, dtype)) != LAB200_OK) return rc;
-  if ((rc = make_tmap(&tm[2], v, bh, n, e, dtype)) != LAB200_OK) return rc;
-  if ((rc = make_tmap(&tm[3], dout, bh, n, e, dtype)) != LAB200_OK) return rc;
-  if ((rc = make_tmap(&tm[4], dk, bh, n, d, dtype)) != LAB200_OK) return rc;
-  if ((rc = make_tmap(&tm[5], dv, bh, n, e, dtype)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[0], q, bh, n, d, dtype, layout, h)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[1], k, bh, n, d, dtype, layout, h)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[2], v, bh, n, e, dtype, layout, h)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[3], dout, bh, n, e, dtype, layout, h)) != LAB200_OK) return rc;
   LaDkdvParams p;
   p.slopes = slopes;
-  p.state_in = nullptr;
+  p.state_in = states;
   p.state_out = nullptr;
+  p.dk_out = dk;
+  p.dv_out = dv;
   p.status = static_cast<int*>(workspace);
   p.n = n; p.h = h; p.d = d; p.e = e;
   p.nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
-  p.blocks_per_chunk = p.nblocks;
+  p.blocks_per_chunk = states ? bpc : p.nblocks;
   p.chunk0 = 0;
-  p.state_slots = 1;
+  p.state_slots = states ? nchunks : 1;
+  p.layout = layout;
   p.wait_budget = WAIT_BUDGET;
   p.trace = g_trace.load(std::memory_order_relaxed);
   p.trace_blocks = g_trace_blocks.load(std::memory_order_relaxed);
-  const dim3 grid(1, 1, bh);
+  const dim3 grid(1, states ? nchunks : 1, bh);
   const bool bf = (dtype == LAB200_BF16);
 #define LAB200_CASE(D_, E_) \
   if (nd == D_ && ne == E_) return bf ? launch_dkdv_one<D_, E_, 1>(tm, p, grid, smem, st) : launch_dkdv_one<D_, E_, 0>(tm, p, grid, smem, st);
@@ -398,6 +409,27 @@ int la_dkdv_impl(const void* q, const void* k, const void* v, const void* dout, 
   LAB200_CASE(2, 2)
 #undef LAB200_CASE
   return LAB200_ERR_SHAPE;
+}
+
+// The whole fused sweep: in chunk mode first the reverse-time state entering every chunk (state-only pass over do and q
+// plus scan, or - resume - taken over from an earlier state-only call on (do, q) and rebased on state_in), then one
+// launch over all chunks. state_in: (bh, d, e) fp32 state entering the sequence from its far end, or nullptr.
+int la_dkdv_full(const void* q, const void* k, const void* v, const void* dout, const float* slopes, void* dk, void* dv,
+                 const float* state_in, void* workspace, size_t workspace_bytes, int bh, int h, int n, int d, int e,
+                 int chunks, int resume, int dtype, cudaStream_t st) {
+  if (!dkdv_shape_ok(d, e)) return LAB200_ERR_SHAPE;
+  const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
+  const int nchunks = chunk_count(bh, n, e, d, chunks);
+  const int bpc = (nblocks + nchunks - 1) / nchunks;
+  if (nchunks > 1) {
+    // chunk states of the product (v, do, q): sum lambda^t q_t^T do_t laid out (d, e), exactly the kernel's dKV
+    int rc = la_generic_impl(nullptr, dout, q, slopes, nullptr, state_in, nullptr, workspace, workspace_bytes, bh, h, n, e, d,
+                             1, 0, chunks, dtype, st, PREFIX_ONLY | (resume ? RESUME : 0));
+    if (rc != LAB200_OK) return rc;
+    const float* states = reinterpret_cast<const float*>(static_cast<const uint8_t*>(workspace) + WS_HEADER);
+    return la_dkdv_impl(q, k, v, dout, slopes, dk, dv, workspace, states, nchunks, bpc, bh, h, n, d, e, dtype, st);
+  }
+  return la_dkdv_impl(q, k, v, dout, slopes, dk, dv, workspace, state_in, 1, nblocks, bh, h, n, d, e, dtype, st);
 }
 
 // A reverse-time sweep starts in the last block; the state arriving there is taken to sit at the end of a full tile.
@@ -418,7 +450,7 @@ int la_validate(const void* a, const void* bm, const void* c, const void* out, c
   // only the pipelined kernel (dk <= 128) reads and writes them
   if (layout && ((bh % h) != 0 || static_cast<long long>(bh) * n >= (1LL << 31) || t.nks > 2 || !use_pipelined_kernel()))
     return LAB200_ERR_SHAPE;
-  if (!bm || !c || (!state_only && (!a || !out)) || (state_only && !state_out)) return LAB200_ERR_SHAPE;
+  if (!bm || !c || (!state_only && (!a || !out)) || (state_only == 1 && !state_out)) return LAB200_ERR_SHAPE;
   if (!aligned16(a) || !aligned16(bm) || !aligned16(c) || !aligned16(out) || !aligned16(state_in) ||
       !aligned16(state_out) || !aligned16(workspace))
     return LAB200_ERR_ALIGN;
@@ -568,6 +600,64 @@ int static_scratch_address(void** out) {
   return LAB200_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Device status without a host synchronisation: after the last launch of an attention call the library copies the
+// call's status word into a slot of a small ring of pinned host memory (one ring per device, allocated on the first
+// attention call on that device). lab200_last_status() scans the ring: a non-zero word means a bounded wait of an
+// EARLIER call ran out. The copy is ordered behind the call's kernels, so the report is one or more calls late.
+// ---------------------------------------------------------------------------------------------
+constexpr int STATUS_RING = 64;
+struct StatusRing {
+  int* slots = nullptr;
+  unsigned next = 0;
+  bool tried = false;
+};
+StatusRing g_status_ring[MAX_DEVICES];
+std::mutex g_status_mutex;
+
+void post_status(const void* workspace, cudaStream_t st) {
+  int dev = -1;
+  if (!workspace || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  StatusRing& ring = g_status_ring[dev];
+  if (!ring.slots && !ring.tried) {
+    ring.tried = true;
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, STATUS_RING * sizeof(int), cudaHostAllocDefault) == cudaSuccess && p) {
+      ring.slots = static_cast<int*>(p);
+      for (int i = 0; i < STATUS_RING; ++i) ring.slots[i] = 0;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  if (!ring.slots) return;
+  int* slot = ring.slots + (ring.next++ % STATUS_RING);
+  if (cudaMemcpyAsync(slot, workspace, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) cudaGetLastError();
+}
+
+int finish_call(int rc, const void* workspace, cudaStream_t st) {
+  if (rc == LAB200_OK) post_status(workspace, st);
+  return rc;
+}
+
+// One CTA that waits, with the same bounded wait the block kernels use, on an mbarrier that nothing ever arrives on, and
+// reports the expiry through the status word: exercises the error path (wait budget -> status word -> host) with no
+// asynchronous copy, tensor-memory allocation or MMA in flight.
+__global__ void la_wait_expiry_kernel(int* status, long long budget) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ int abort_flag;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = lap_wait(bar, 0, &abort_flag, budget);
+  __syncthreads();
+  if (threadIdx.x == 0 && !ok) atomicExch(status, LA_ERR_WAIT_INPUT);
+}
+
 }  // namespace
 
 extern "C" {
@@ -618,8 +708,8 @@ int lab200_la_generic(const void* a, const void* bm, const void* c, const float*
   if (rc != LAB200_OK) return rc;
   if (!reverse_chain_ok(reverse, state_in, n)) return LAB200_ERR_SHAPE;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
-  return la_generic_impl(a, bm, c, slopes, out, state_in, state_out, workspace, workspace_bytes, bh, h, n, dk, dv,
-                         reverse, state_only, chunks, dtype, st);
+  return finish_call(la_generic_impl(a, bm, c, slopes, out, state_in, state_out, workspace, workspace_bytes, bh, h, n, dk, dv,
+                         reverse, state_only, chunks, dtype, st), workspace, st);
 }
 
 int lab200_la_generic_resume(const void* a, const void* bm, const void* c, const float* slopes, void* out,
@@ -630,8 +720,8 @@ int lab200_la_generic_resume(const void* a, const void* bm, const void* c, const
   if (rc != LAB200_OK) return rc;
   if (!reverse_chain_ok(reverse, state_in, n)) return LAB200_ERR_SHAPE;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
-  return la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
-                         chunks, dtype, st, RESUME);
+  return finish_call(la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
+                         chunks, dtype, st, RESUME), workspace, st);
 }
 
 int lab200_la_generic_resume_swapped(const void* a, const void* bm, const void* c, const float* slopes, void* out,
@@ -643,8 +733,8 @@ int lab200_la_generic_resume_swapped(const void* a, const void* bm, const void* 
   if (rc != LAB200_OK) return rc;
   if (!reverse_chain_ok(reverse, state_in, n)) return LAB200_ERR_SHAPE;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
-  return la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
-                         chunks, dtype, st, RESUME | RESUME_SWAPPED | (rebase ? 0 : RESUME_NO_REBASE));
+  return finish_call(la_generic_impl(a, bm, c, slopes, out, state_in, nullptr, workspace, workspace_bytes, bh, h, n, dk, dv, reverse, 0,
+                         chunks, dtype, st, RESUME | RESUME_SWAPPED | (rebase ? 0 : RESUME_NO_REBASE)), workspace, st);
 }
 
 int lab200_la_combine_states(const float* gathered, const float* slopes, float* out, float* out_t, int ranks, int rank,
@@ -685,8 +775,8 @@ int lab200_la2_fwd(const void* q, const void* k, const void* v, const float* slo
   int rc = la_validate(q, k, v, o, nullptr, nullptr, workspace, b * h, h, n, d, e, 0, dtype);
   if (rc != LAB200_OK) return rc;
   if ((rc = reset_status(workspace, workspace_bytes, st)) != LAB200_OK) return rc;
-  return la_generic_impl(q, k, v, slopes, o, nullptr, nullptr, workspace, workspace_bytes, b * h, h, n, d, e, 0, 0,
-                         chunks, dtype, st);
+  return finish_call(la_generic_impl(q, k, v, slopes, o, nullptr, nullptr, workspace, workspace_bytes, b * h, h, n, d, e, 0, 0,
+                         chunks, dtype, st), workspace, st);
 }
 
 int lab200_la2_fwd_static(const void* q, const void* k, const void* v, const float* slopes, void* o, int b, int h,
@@ -708,7 +798,7 @@ int lab200_la2_fwd_static(const void* q, const void* k, const void* v, const flo
                          0, 0, chunks, dtype, st);
 }
 
-int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dq,
+static int la2_bwd_body(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dq,
                    void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h, int n, int d, int e,
                    int chunks, int dtype, void* stream) {
   if (b < 1 || h < 1 || b > 65535 / h) return LAB200_ERR_SHAPE;
@@ -724,15 +814,10 @@ int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slo
                        chunks, dtype, st);
   if (rc != LAB200_OK) return rc;
   // dk_t = sum_{j>=t} lambda^(j-t) (v_t . do_j) q_j  and  dv_t = sum_{j>=t} lambda^(j-t) (k_t . q_j) do_j:
-  // one fused reverse sweep when every (batch, head) pair gets one CTA, else two launches of the generic kernel
-  {
-    const int nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;
-    int nchunks = chunks > 0 ? chunks : plan_chunks(bh, n, e, d);
-    if (nchunks > nblocks) nchunks = nblocks;
-    if (nchunks == 1 && use_fused_dkdv() && !(dtype & LAB200_LAYOUT_BNHD)) {
-      rc = la_dkdv_impl(q, k, v, dout, slopes, dk, dv, workspace, bh, h, n, d, e, dtype, st);
-      if (rc != LAB200_ERR_SHAPE) return rc;
-    }
+  // one fused reverse sweep (d, e <= 128), else two launches of the generic kernel
+  if (use_fused_dkdv() && dkdv_shape_ok(d, e)) {
+    rc = la_dkdv_full(q, k, v, dout, slopes, dk, dv, nullptr, workspace, workspace_bytes, bh, h, n, d, e, chunks, 0, dtype, st);
+    if (rc != LAB200_ERR_SHAPE) return rc;
   }
   rc = la_generic_impl(v, dout, q, slopes, dk, nullptr, nullptr, workspace, workspace_bytes, bh, h, n, e, d, 1, 0,
                        chunks, dtype, st);
@@ -744,20 +829,39 @@ int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slo
                          chunks, dtype, st, resume);
 }
 
+int lab200_la2_bwd(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dq,
+                   void* dk, void* dv, void* workspace, size_t workspace_bytes, int b, int h, int n, int d, int e,
+                   int chunks, int dtype, void* stream) {
+  return finish_call(la2_bwd_body(q, k, v, slopes, dout, dq, dk, dv, workspace, workspace_bytes, b, h, n, d, e, chunks, dtype,
+                                  stream),
+                     workspace, static_cast<cudaStream_t>(stream));
+}
+
+size_t lab200_la2_bwd_workspace_bytes(int b, int h, int n, int d, int e, int chunks) {
+  if (b < 1 || h < 1) return WS_HEADER;
+  // the three products inside lab200_la2_bwd run as (dk, dv) = (e, d) for dq and dk and (d, e) for dv; each plans its own chunks
+  const size_t x = lab200_la_workspace_bytes(b * h, n, e, d, chunks), y = lab200_la_workspace_bytes(b * h, n, d, e, chunks);
+  return x > y ? x : y;
+}
+
 int lab200_la2_dkdv(const void* q, const void* k, const void* v, const float* slopes, const void* dout, void* dk,
-                    void* dv, void* workspace, size_t workspace_bytes, int b, int h, int n, int d, int e, int dtype,
-                    void* stream) {
+                    void* dv, const float* state_in, void* workspace, size_t workspace_bytes, int b, int h, int n, int d,
+                    int e, int chunks, int resume, int dtype, void* stream) {
   if (b < 1 || h < 1 || b > 65535 / h || n < 1) return LAB200_ERR_SHAPE;
-  if (dtype != LAB200_BF16 && dtype != LAB200_F16) return LAB200_ERR_DTYPE;
+  const int dt = dtype & 0xff;
+  if (dt != LAB200_BF16 && dt != LAB200_F16) return LAB200_ERR_DTYPE;
   if (!q || !k || !v || !dout || !dk || !dv) return LAB200_ERR_SHAPE;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dk) || !aligned16(dv) ||
-      !aligned16(workspace))
+      !aligned16(workspace) || !aligned16(state_in))
     return LAB200_ERR_ALIGN;
-  if (d > 128 || e > 128 || (d % 16) || (e % 16) || d < 16 || e < 16) return LAB200_ERR_SHAPE;
+  if (!dkdv_shape_ok(d, e)) return LAB200_ERR_SHAPE;
+  if ((dtype & LAB200_LAYOUT_BNHD) && static_cast<long long>(b) * h * n >= (1LL << 31)) return LAB200_ERR_SHAPE;
+  if (!reverse_chain_ok(1, state_in, n)) return LAB200_ERR_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = reset_status(workspace, workspace_bytes, st);
   if (rc != LAB200_OK) return rc;
-  return la_dkdv_impl(q, k, v, dout, slopes, dk, dv, workspace, b * h, h, n, d, e, dtype, st);
+  return finish_call(la_dkdv_full(q, k, v, dout, slopes, dk, dv, state_in, workspace, workspace_bytes, b * h, h, n, d, e, chunks,
+                      resume, dtype, st), workspace, st);
 }
 
 int lab200_read_status(const void* workspace, void* stream) {
@@ -767,6 +871,40 @@ int lab200_read_status(const void* workspace, void* stream) {
   if (cudaMemcpyAsync(&v, workspace, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -2;
   if (cudaStreamSynchronize(st) != cudaSuccess) return -3;
   return v;
+}
+
+int lab200_last_status(void) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  StatusRing& ring = g_status_ring[dev];
+  if (!ring.slots) return 0;
+  for (int i = 0; i < STATUS_RING; ++i) {
+    const int v = *const_cast<volatile int*>(ring.slots + i);
+    if (v != 0) {
+      ring.slots[i] = 0;
+      return v;
+    }
+  }
+  return 0;
+}
+
+int lab200_static_status(void* stream) {
+  void* scratch = nullptr;
+  if (static_scratch_address(&scratch) != LAB200_OK) return -1;
+  return lab200_read_status(scratch, stream);
+}
+
+int lab200_debug_wait_expiry(void* workspace, size_t workspace_bytes, long long budget_cycles, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (budget_cycles < 1 || budget_cycles > 100000000LL) return LAB200_ERR_SHAPE;  // at most ~50 ms of SM clocks
+  int rc = reset_status(workspace, workspace_bytes, st);
+  if (rc != LAB200_OK) return rc;
+  la_wait_expiry_kernel<<<1, 32, 0, st>>>(static_cast<int*>(workspace), budget_cycles);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (cudaGetLastError() != cudaSuccess) return LAB200_ERR_CUDA;
+  post_status(workspace, st);
+  return LAB200_OK;
 }
 
 int lab200_srmsnorm_fwd(const void* x, void* y, float* rstd, long long M, int N, float eps, int dtype, void* stream) {

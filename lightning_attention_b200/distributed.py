@@ -100,14 +100,6 @@ def combine_states(states, decay, rank, reverse=False):
     return torch.einsum("rh,rbhxy->bhxy", w, stacked.to(torch.float32)).to(stacked.dtype)
 
 
-def exchange_states(local_state, group=None):
-    """All-gather of the per-rank local states (each (b, h, x, y) fp32). Returns the list indexed by rank."""
-    world = dist.get_world_size(group)
-    out = [torch.empty_like(local_state) for _ in range(world)]
-    dist.all_gather(out, local_state.contiguous(), group=group)
-    return out
-
-
 def gather_states(local_state, group=None):
     """All-gather of the per-rank local states into ONE tensor (world, b, h, x, y): a single collective, no copies."""
     world = dist.get_world_size(group)
@@ -149,7 +141,7 @@ def _default_product():
 
 class _SequenceParallelAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, s, group, product):
+    def forward(ctx, q, k, v, s, group, product, dkdv):
         b, h, L, d = q.shape
         if L % BLOCK != 0:
             raise RuntimeError(f"sequence-parallel shards must be multiples of {BLOCK} tokens, got {L}")
@@ -161,7 +153,7 @@ class _SequenceParallelAttention(torch.autograd.Function):
         o, _, handle = product(q, k, v, s, reverse=False, state_in=kv_in, resume_from=handle, keep_workspace=True)
         ctx.save_for_backward(q, k, v, s if s is not None else torch.empty(0), kv_in_t)
         ctx.has_s = s is not None
-        ctx.group, ctx.product = group, product
+        ctx.group, ctx.product, ctx.dkdv = group, product, dkdv
         ctx.kv_handle = handle if d == v.shape[-1] else None  # chunk states of (k, v), incoming state included
         return o
 
@@ -184,20 +176,29 @@ class _SequenceParallelAttention(torch.autograd.Function):
         # reverse-time state of this shard for dk: (b, h, d, e) = sum_t lambda^t q_t^T do_t
         _, ds_loc, handle = product(None, do, q, s, reverse=True, state_only=True, keep_workspace=True)
         dkv_in, dkv_in_t = combine_gathered(gather_states(ds_loc, group), s, L, rank, reverse=True)
+        if ctx.dkdv is not None:  # one fused sweep for dk and dv; the kept chunk states of (do, q) are rebased on dkv_in
+            dk, dv = ctx.dkdv(q, k, v, s, do, state_in=dkv_in, resume_from=handle)
+            return dq, dk, dv, None, None, None, None
         dk, _, handle = product(v, do, q, s, reverse=True, state_in=dkv_in, resume_from=handle, keep_workspace=True)
         if d == v.shape[-1]:
             dv, _ = product(k, q, do, s, reverse=True, state_in=dkv_in_t, resume_from=handle, resume_swapped=True, rebase=False)
         else:
             dv, _ = product(k, q, do, s, reverse=True, state_in=dkv_in_t)
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
-def lightning_attn_sp(q, k, v, s=None, group=None, product=None):
+def lightning_attn_sp(q, k, v, s=None, group=None, product=None, dkdv=None):
     """Sequence-parallel lightning attention. q, k (b, h, L, d) and v (b, h, L, e) are this rank's contiguous
     shard of the sequence (rank r holds tokens [r L, (r+1) L)); returns this rank's shard of o. Differentiable
-    w.r.t. q, k, v; two all-gathers of (b, h, d, e) fp32 states per forward+backward."""
+    w.r.t. q, k, v; two all-gathers of (b, h, d, e) fp32 states per forward+backward.
+    `product` / `dkdv`: implementations of the generic product and of the fused dk+dv sweep (signatures of `la_generic` and
+    `la_dkdv`); default: the CUDA ops, with the fused sweep wherever it covers the shape."""
     if not dist.is_initialized():
         raise RuntimeError("lightning_attn_sp needs an initialised torch.distributed process group")
     if product is None:
         product = _default_product()
-    return _SequenceParallelAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), s, group, product)
+        from .ops.cuda.lightning_attn2 import dkdv_fused_supported, la_dkdv
+
+        if dkdv is None and dkdv_fused_supported(q.shape[-1], v.shape[-1]):
+            dkdv = la_dkdv
+    return _SequenceParallelAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), s, group, product, dkdv)

@@ -8,6 +8,7 @@ from .cuda import (  # noqa: F401
     LightningAttention2NoDecay,
     SimpleRMSNorm,
     la_generic,
+    la_dkdv,
     lightning_attn_prefill,
     lightning_attn_decode,
     srmsnorm_sigmoid_gate,
@@ -16,5 +17,5 @@ from .cuda import (  # noqa: F401
 __all__ = [
     "lightning_attn_func", "is_support", "next_power_of_2", "linear_attn", "SimpleRMSNormTorch",
     "lightning_attn2", "lightning_attn2_no_decay", "lightning_attn2_parallel", "LightningAttention2",
-    "LightningAttention2NoDecay", "SimpleRMSNorm", "la_generic", "lightning_attn_prefill", "lightning_attn_decode", "srmsnorm_sigmoid_gate",
+    "LightningAttention2NoDecay", "SimpleRMSNorm", "la_generic", "la_dkdv", "lightning_attn_prefill", "lightning_attn_decode", "srmsnorm_sigmoid_gate",
 ]

@@ -5,6 +5,7 @@ from .lightning_attn2 import (  # noqa: F401
     lightning_attn2_no_decay,
     lightning_attn2_parallel,
     la_generic,
+    la_dkdv,
     lightning_attn_prefill,
     lightning_attn_decode,
 )

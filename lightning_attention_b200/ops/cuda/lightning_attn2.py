@@ -94,6 +94,7 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
     Any call with keep_workspace=True returns (out, state_out, handle).
     """
     _lib.require_cuda(a, bm, c)
+    _lib.raise_on_device_status(bm.device)
     b, h, n, dk = bm.shape
     dv = c.shape[-1]
     dev = bm.device
@@ -141,9 +142,9 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
             return out, None, hd
         return out, None
     state_out = torch.empty((b, h, dv, dk), dtype=torch.float32, device=dev) if (want_state or state_only) else None
-    nbytes = L.lab200_la_workspace_bytes(b * h, n, dk, dv, chunks)
-    ws = _workspace(nbytes, dev)
     with torch.cuda.device(dev):
+        nbytes = L.lab200_la_workspace_bytes(b * h, n, dk, dv, chunks)
+        ws = _workspace(nbytes, dev)
         rc = L.lab200_la_generic(
             _lib.ptr(a), _lib.ptr(bm), _lib.ptr(c), _lib.ptr(sl), _lib.ptr(out), _lib.ptr(state_in),
             _lib.ptr(state_out), ws.data_ptr(), nbytes, b * h, h, n, dk, dv, int(bool(reverse)),
@@ -154,15 +155,63 @@ def la_generic(a, bm, c, s=None, reverse=False, state_in=None, want_state=False,
     return out, state_out
 
 
+def dkdv_fused_supported(d, e):
+    """Shapes the fused dk+dv sweep (lab200_la2_dkdv) covers."""
+    return d % 16 == 0 and e % 16 == 0 and 16 <= d <= 128 and 16 <= e <= 128
+
+
+def la_dkdv(q, k, v, s, do, state_in=None, chunks=0, resume_from=None):
+    """dk and dv of the backward pass in one fused reverse-time sweep (lab200_la2_dkdv): q, k, v, do are read once.
+
+    q, k: (b, h, n, d); v, do: (b, h, n, e); d, e <= 128. state_in: optional (b, h, d, e) fp32 reverse-time state
+    sum_t lambda^t q_t^T do_t arriving from tokens after the end of the sequence (sequence parallelism).
+    resume_from: handle of `la_generic(None, do, q, s, reverse=True, state_only=True, keep_workspace=True, chunks=chunks)`;
+    its per-chunk states are reused (the state-only pass over do and q is not repeated). Returns (dk, dv)."""
+    _lib.require_cuda(q, k, v, do)
+    _lib.raise_on_device_status(q.device)
+    b, h, n, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    bnhd = _use_bnhd(q, k, v, do)
+    if resume_from is not None and not bnhd and not (do.is_contiguous() and q.is_contiguous()):
+        raise RuntimeError("resume_from needs do and q in one of the two layouts the library reads in place")
+    q, k, v, do = (_to_layout(t, bnhd) for t in (q, k, v, do))
+    sl = _slopes_arg(s, h, dev)
+    dk = _empty_out(b, h, n, d, q.dtype, dev, bnhd)
+    dv = _empty_out(b, h, n, e, q.dtype, dev, bnhd)
+    dt = _lib.dtype_code(q.dtype) | (LAYOUT_BNHD if bnhd else 0)
+    if state_in is not None:
+        state_in = state_in.to(device=dev, dtype=torch.float32).contiguous()
+        if tuple(state_in.shape) != (b, h, d, e):
+            raise RuntimeError(f"state_in must have shape {(b, h, d, e)}, got {tuple(state_in.shape)}")
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        if resume_from is not None:
+            hd = resume_from
+            if not isinstance(hd, KeptWorkspace) or hd.key != _product_key(do, q, True, chunks) or hd.based:
+                raise RuntimeError("resume_from does not come from a state-only reverse-time call on (do, q) with the same options")
+            ws, nbytes, resume = hd.ws, hd.nbytes, 1
+            hd.based = True  # used up: the states now include the incoming state
+        else:
+            nbytes = L.lab200_la_workspace_bytes(b * h, n, e, d, chunks)
+            ws, resume = _workspace(nbytes, dev), 0
+        rc = L.lab200_la2_dkdv(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), do.data_ptr(), dk.data_ptr(),
+                               dv.data_ptr(), _lib.ptr(state_in), ws.data_ptr(), nbytes, b, h, n, d, e, int(chunks), resume,
+                               dt, _lib.stream_ptr(dev))
+    _lib.check(rc, "lab200_la2_dkdv")
+    return dk, dv
+
+
 def _fwd(q, k, v, sl, chunks=0, bnhd=False):
     """q, k, v all in one layout: (b, h, n, dim) contiguous, or (bnhd=True) views of (b, n, h, dim) tensors."""
     b, h, n, d = q.shape
     e = v.shape[-1]
     o = _empty_out(b, h, n, e, q.dtype, q.device, bnhd)
+    _lib.raise_on_device_status(q.device)
     L = _lib.lib()
-    nbytes = L.lab200_la_workspace_bytes(b * h, n, d, e, chunks)
-    ws = _workspace(nbytes, q.device)
     with torch.cuda.device(q.device):
+        nbytes = L.lab200_la_workspace_bytes(b * h, n, d, e, chunks)
+        ws = _workspace(nbytes, q.device)
         rc = L.lab200_la2_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), o.data_ptr(), ws.data_ptr(),
                               nbytes, b, h, n, d, e, int(chunks), _lib.dtype_code(q.dtype) | (LAYOUT_BNHD if bnhd else 0),
                               _lib.stream_ptr(q.device))
@@ -176,11 +225,11 @@ def _bwd(q, k, v, sl, do, chunks=0, bnhd=False):
     dq = _empty_out(b, h, n, d, q.dtype, q.device, bnhd)
     dk = _empty_out(b, h, n, d, q.dtype, q.device, bnhd)
     dv = _empty_out(b, h, n, e, q.dtype, q.device, bnhd)
+    _lib.raise_on_device_status(q.device)
     L = _lib.lib()
-    m = max(d, e)
-    nbytes = L.lab200_la_workspace_bytes(b * h, n, m, m, chunks)
-    ws = _workspace(nbytes, q.device)
-    with torch.cuda.device(q.device):
+    with torch.cuda.device(q.device):  # the chunk plan depends on the SM count of the tensors' device
+        nbytes = L.lab200_la2_bwd_workspace_bytes(b, h, n, d, e, chunks)
+        ws = _workspace(nbytes, q.device)
         rc = L.lab200_la2_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), do.data_ptr(), dq.data_ptr(),
                               dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), nbytes, b, h, n, d, e, int(chunks),
                               _lib.dtype_code(q.dtype) | (LAYOUT_BNHD if bnhd else 0), _lib.stream_ptr(q.device))
@@ -193,7 +242,8 @@ def _chunked(q, v):
     chunk states of one product can be handed to the product with k and v exchanged instead of being recomputed."""
     b, h, n, d = q.shape
     e = v.shape[-1]
-    return d == e and _lib.lib().lab200_la_plan_chunks(b * h, n, d, e) > 1
+    with torch.cuda.device(q.device):
+        return d == e and _lib.lib().lab200_la_plan_chunks(b * h, n, d, e) > 1
 
 
 def _fwd_keep(q, k, v, s):
@@ -206,6 +256,8 @@ def _bwd_from_kept(q, k, v, s, do, handle):
     """Backward in chunk mode with d == e: dq takes the forward's chunk states transposed, dv takes dk's; only dk's
     (reverse-time sums of q^T do) are computed here."""
     dq, _ = la_generic(do, v, k, s, resume_from=handle, resume_swapped=True, rebase=False)
+    if dkdv_fused_supported(q.shape[-1], v.shape[-1]):
+        return (dq,) + la_dkdv(q, k, v, s, do)
     dk, _, h2 = la_generic(v, do, q, s, reverse=True, keep_workspace=True)
     dv, _ = la_generic(k, q, do, s, reverse=True, resume_from=h2, resume_swapped=True, rebase=False)
     return dq, dk, dv
@@ -217,6 +269,11 @@ def _check_inputs(q, k, v):
         raise RuntimeError(f"expected q, k (b, h, n, d) and v (b, h, n, e); got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
     if not (q.dtype == k.dtype == v.dtype):
         raise RuntimeError("q, k, v must share one dtype")
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        # the reference's Triton kernels also take fp32 tensors (they compute in fp32 anyway); the tensor-core kernels
+        # here read 16-bit operands only, and silently down-casting a caller's fp32 tensors would change its results
+        raise RuntimeError(f"lightning attention takes bf16 or fp16 tensors, got {q.dtype}; cast q, k, v first "
+                           "(e.g. q.bfloat16()) - accumulation and the running state are fp32 either way")
 
 
 class LightningAttention2(torch.autograd.Function):

@@ -58,8 +58,8 @@ class _SrmsNormGate(torch.autograd.Function):
         if x.dtype == torch.float16:
             eps = max(eps, 1.6e-5)
         N = x.shape[-1]
-        x_arg = x.reshape(-1, N).contiguous()
-        g_arg = gate.reshape(-1, N).contiguous()
+        x_arg = _aligned16(x.reshape(-1, N).contiguous())
+        g_arg = _aligned16(gate.reshape(-1, N).contiguous())
         M = x_arg.shape[0]
         y = torch.empty_like(x_arg)
         rstd = torch.empty((M,), dtype=torch.float32, device=x.device)
@@ -77,6 +77,7 @@ class _SrmsNormGate(torch.autograd.Function):
         dy_arg = dy.reshape(-1, N).contiguous()
         if dy_arg.dtype != x.dtype:
             dy_arg = dy_arg.to(x.dtype)
+        dy_arg = _aligned16(dy_arg)
         dx = torch.empty_like(x)
         dg = torch.empty_like(x)
         with torch.cuda.device(x.device):
@@ -85,6 +86,12 @@ class _SrmsNormGate(torch.autograd.Function):
                                                      _lib.stream_ptr(x.device))
         _lib.check(rc, "lab200_srmsnorm_gate_bwd")
         return dx.reshape(dy.shape), dg.reshape(dy.shape), None
+
+
+def _aligned16(t):
+    """The fused kernels use 128-bit loads: a contiguous view whose storage offset is not 16-byte aligned (a slice of a flat
+    buffer) is copied once; fresh allocations are always aligned."""
+    return t if t.data_ptr() % 16 == 0 else t.clone()
 
 
 def _gate_rows_supported(x):

@@ -2,11 +2,13 @@
 
 The reference pads e to a power of two and splits d > 128 into 64-wide slices whose partial
 outputs it sums, because its Triton kernels need power-of-two tiles. The CUDA kernels take any
-d <= 256 and any e that are multiples of 16, so here padding only happens for sizes that are not
-multiples of 16, and splitting only for d > 256 (the product q.k is additive over feature slices).
+d <= 256 and e <= 256 that are multiples of 16, so here padding only happens for sizes that are not
+multiples of 16, and splitting only for d > 256 (the product q.k is additive over feature slices) and
+e > 256 (output columns are independent).
 """
 import math
 
+import torch
 import torch.nn.functional as F
 
 from .cuda import lightning_attn2, lightning_attn2_no_decay
@@ -42,13 +44,21 @@ def lightning_attn_func(q, k, v, s=None, variant="chunk_loop"):
     v = _pad_last(v, 16)
     d = q.shape[-1]
 
-    def fn(q1, k1):
-        return lightning_attn2_no_decay(q1, k1, v) if s is None else lightning_attn2(q1, k1, v, s)
+    def fn(q1, k1, v1):
+        return lightning_attn2_no_decay(q1, k1, v1) if s is None else lightning_attn2(q1, k1, v1, s)
 
-    if d > _MAX_D:
-        o = 0
+    def over_d(v1):
+        if d <= _MAX_D:
+            return fn(q, k, v1)
+        o1 = 0
         for start in range(0, d, _MAX_D):
-            o = o + fn(q[..., start:start + _MAX_D], k[..., start:start + _MAX_D])
+            o1 = o1 + fn(q[..., start:start + _MAX_D], k[..., start:start + _MAX_D], v1)
+        return o1
+
+    # output columns are independent of each other: e > 256 (which the backward kernels do not take as one piece, its dq
+    # contracts over e) runs as column slices of v whose outputs are concatenated; autograd sums their dq, dk
+    if v.shape[-1] > _MAX_D:
+        o = torch.cat([over_d(v[..., start:start + _MAX_D]) for start in range(0, v.shape[-1], _MAX_D)], dim=-1)
     else:
-        o = fn(q, k)
+        o = over_d(v)
     return o[..., :e] if o.shape[-1] != e else o

@@ -60,9 +60,9 @@ def test_reference_shape_list_bf16(cuda_lib, b, h, n, d, e):
     compare_with_torch_reference(q, k, v, do, s, got, True, f"decay{(b, h, n, d, e)}")
 
 
-@pytest.mark.parametrize("b,h,n,d,e", [REF_SHAPES[i] for i in (0, 3, 6, 7, 11, 14, 17)])
+@pytest.mark.parametrize("b,h,n,d,e", REF_SHAPES)
 def test_reference_shape_list_fp16(cuda_lib, b, h, n, d, e):
-    """The reference's second dtype (tests/ops/test_lightning2.py:35), subset of its shape list. fp16 rounds finer than
+    """The reference's second dtype (tests/ops/test_lightning2.py:35), all 18 shapes. fp16 rounds finer than
     bf16, so the same tolerance applies with room to spare; the running state is carried in fp32 and only its
     tensor-core copy is fp16, which randn/10 inputs keep far from the fp16 range limit."""
     q, k, v, do = make_inputs(b, h, n, d, e, torch.float16, 0.1)
@@ -71,10 +71,11 @@ def test_reference_shape_list_fp16(cuda_lib, b, h, n, d, e):
     compare_with_torch_reference(q, k, v, do, s, got, True, f"fp16{(b, h, n, d, e)}")
 
 
-@pytest.mark.parametrize("b,h,n,d,e", [REF_SHAPES[i] for i in (0, 3, 6, 14, 15, 17)])
-def test_reference_shape_list_no_decay_bf16(cuda_lib, b, h, n, d, e):
-    """tests/ops/test_lightning2_no_decay.py:31-56 (s=None), subset of its shape list."""
-    q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 0.1)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,h,n,d,e", REF_SHAPES)
+def test_reference_shape_list_no_decay(cuda_lib, b, h, n, d, e, dtype):
+    """tests/ops/test_lightning2_no_decay.py:8-56 (s=None): all 18 shapes, both dtypes."""
+    q, k, v, do = make_inputs(b, h, n, d, e, dtype, 0.1)
     got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2_no_decay(a, b_, c), q, k, v, do)
     compare_with_torch_reference(q, k, v, do, None, got, True, f"nodecay{(b, h, n, d, e)}")
 
@@ -292,30 +293,68 @@ def test_sequence_parallel_math_on_one_gpu(cuda_lib, scale):
         assert_parity(x, r_, f"sp-emulated:{name}", False)
 
 
+@pytest.mark.parametrize("chunks", [1, 3])
 @pytest.mark.parametrize("b,h,n,d,e,decay", [(2, 4, 1024, 128, 128, True), (1, 3, 513, 128, 64, True), (2, 2, 300, 64, 128, True),
-                                             (1, 2, 77, 32, 16, True), (1, 4, 2048, 128, 128, False), (1, 2, 128, 16, 16, True)])
-def test_fused_dk_dv_sweep(cuda_lib, b, h, n, d, e, decay):
-    """lab200_la2_dkdv (dk and dv in one reverse sweep) against the fp32 reference gradients and against the dk, dv that
-    lab200_la2_bwd produces with the generic kernel."""
+                                             (1, 2, 77, 32, 16, True), (1, 4, 2048, 128, 128, False), (1, 2, 128, 16, 16, True),
+                                             (1, 2, 640, 96, 112, True)])
+def test_fused_dk_dv_sweep(cuda_lib, b, h, n, d, e, decay, chunks):
+    """lab200_la2_dkdv (dk and dv in one reverse sweep, one chunk or several) through the C ABI against the fp32 reference
+    gradients and against the dk, dv of two launches of the generic kernel."""
     q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 1.0)
     s = la._build_slope_tensor(h).to(DEV) if decay else None
     sl = None if s is None else s.reshape(-1).contiguous()
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
-    ws = torch.empty(256, dtype=torch.uint8, device=DEV)
+    nbytes = cuda_lib.lab200_la_workspace_bytes(b * h, n, e, d, chunks)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
     stream = torch.cuda.current_stream().cuda_stream
     rc = cuda_lib.lab200_la2_dkdv(q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(sl), do.data_ptr(), dk.data_ptr(),
-                                  dv.data_ptr(), ws.data_ptr(), 256, b, h, n, d, e, _lib.BF16, stream)
+                                  dv.data_ptr(), None, ws.data_ptr(), nbytes, b, h, n, d, e, chunks, 0, _lib.BF16, stream)
     assert rc == 0, cuda_lib.lab200_error_string(rc)
     assert cuda_lib.lab200_read_status(ws.data_ptr(), stream) == 0
     qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
     _, _, rdk, rdv = run_fwd_bwd(lambda a, b_, c: torch_la_reference(a, b_, c, s), qr, kr, vr, do.float())
     assert_parity(dk, rdk, "fused:dk", False)
     assert_parity(dv, rdv, "fused:dv", False)
-    fn = (lambda a, b_, c: la.lightning_attn2(a, b_, c, s)) if decay else (lambda a, b_, c: la.lightning_attn2_no_decay(a, b_, c))
-    _, _, gdk, gdv = run_fwd_bwd(fn, q, k, v, do)
+    gdk, _ = la_generic(v.detach(), do, q.detach(), s, reverse=True, chunks=chunks)
+    gdv, _ = la_generic(k.detach(), q.detach(), do, s, reverse=True, chunks=chunks)
     assert_parity(dk, gdk.float(), "fused-vs-generic:dk", False)
     assert_parity(dv, gdv.float(), "fused-vs-generic:dv", False)
+
+
+@pytest.mark.parametrize("chunks", [1, 2])
+@pytest.mark.parametrize("scale", [1.0, 1e-2])
+def test_fused_dk_dv_with_incoming_state_and_kept_chunk_states(cuda_lib, chunks, scale):
+    """The sequence-parallel use of the fused sweep: the second half of a sequence, given the reverse-time state that its
+    (absent) continuation contributes, equals the matching rows of the whole sequence; with and without the two-step
+    protocol that reuses the chunk states of a state-only call on (do, q)."""
+    b, h, n, d, e = 1, 4, 1024, 128, 64
+    q, k, v, do = (t.detach() for t in make_inputs(b, h, n, d, e, torch.bfloat16, 1.0, seed=11))
+    s = la._build_slope_tensor(h).to(DEV) * scale
+    whole_dk, whole_dv = la.la_dkdv(q, k, v, s, do)
+    half = n // 2
+    lo = lambda t: t[:, :, :half].contiguous()
+    hi = lambda t: t[:, :, half:].contiguous()
+    _, tail_state = la_generic(None, hi(do), hi(q), s, reverse=True, state_only=True)  # (b, h, d, e): what tokens >= half contribute
+    dk1, dv1 = la.la_dkdv(lo(q), lo(k), lo(v), s, lo(do), state_in=tail_state, chunks=chunks)
+    do_lo, q_lo = lo(do), lo(q)
+    _, _, handle = la_generic(None, do_lo, q_lo, s, reverse=True, state_only=True, keep_workspace=True, chunks=chunks)
+    dk2, dv2 = la.la_dkdv(q_lo, lo(k), lo(v), s, do_lo, state_in=tail_state, chunks=chunks, resume_from=handle)
+    for got_k, got_v, tag in ((dk1, dv1, "direct"), (dk2, dv2, "resumed")):
+        assert_parity(got_k, whole_dk[:, :, :half].float(), f"fused-state-{tag}:dk", False)
+        assert_parity(got_v, whole_dv[:, :, :half].float(), f"fused-state-{tag}:dv", False)
+
+
+def test_fused_dk_dv_reads_and_writes_the_projection_layout(cuda_lib):
+    """(b, n, h, dim) tensors in place: bit-identical to the default layout."""
+    b, h, n, d, e = 2, 4, 640, 128, 128
+    q, k, v, do = (t.detach() for t in make_inputs(b, h, n, d, e, torch.bfloat16, 1.0, seed=12))
+    s = la._build_slope_tensor(h).to(DEV)
+    dk, dv = la.la_dkdv(q, k, v, s, do)
+    view = lambda t: t.transpose(1, 2).contiguous().transpose(1, 2)  # same values, (b, n, h, dim) storage
+    dk2, dv2 = la.la_dkdv(view(q), view(k), view(v), s, view(do))
+    assert dk2.stride() == view(q).stride() and dv2.stride() == view(v).stride()
+    assert torch.equal(dk2, dk) and torch.equal(dv2, dv)
 
 
 @pytest.mark.parametrize("reverse", [False, True])
@@ -562,3 +601,79 @@ def test_randomised_shapes_against_numpy_oracle(cuda_lib, seed):
     assert O.max_abs_err(f(out), ro) <= 2e-2 * max(1.0, float(np.abs(ro).max())), tag
     if want_state:
         assert O.rel_l2_err(f(st), rs) <= 1e-2, tag
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# long sequences where the running state never dies out (no decay, very slow decay): error growth with n
+# ------------------------------------------------------------------------------------------------------------------
+LONG_N_RESULTS = {}
+
+
+@pytest.mark.parametrize("variant", ["no_decay", "slopes_x1e-3", "alibi"])
+@pytest.mark.parametrize("n", [2048, 8192, 32768, 131072])
+def test_long_sequences_with_a_state_that_never_dies(cuda_lib, n, variant):
+    """b1 h4 d=e=128 bf16, q, k, v ~ 0.5 N(0,1): no decay, ALiBi slopes x 1e-3 and ALiBi slopes at n up to 131072 (chunk mode:
+    4 pairs on 148 SMs) against the fp32 block recurrence. The state is carried in fp32 but fed to the tensor cores as a
+    bf16 copy, so this is where a rounding error that grows with n would show."""
+    b, h, d = 1, 4, 128
+    q, k, v, do = make_inputs(b, h, n, d, d, torch.bfloat16, 0.5, seed=31)
+    s = None if variant == "no_decay" else la._build_slope_tensor(h).to(DEV) * (1e-3 if variant == "slopes_x1e-3" else 1.0)
+    fn = (lambda a, b_, c: la.lightning_attn2_no_decay(a, b_, c)) if s is None else (lambda a, b_, c: la.lightning_attn2(a, b_, c, s))
+    got = run_fwd_bwd(fn, q, k, v, do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = run_fwd_bwd(lambda a, b_, c: torch_la_reference(a, b_, c, s), qr, kr, vr, do.float())
+    rels = {}
+    for x, r, name in zip(got, ref, ("o", "dq", "dk", "dv")):
+        rels[name] = errs(x, r)[1]
+        assert_parity(x, r, f"long-{variant}-n{n}:{name}", False)
+    LONG_N_RESULTS[(variant, n)] = rels
+    print(f"rel-L2 {variant} n={n}: " + " ".join(f"{k_}={v_:.2e}" for k_, v_ in rels.items()))
+
+
+def test_backward_with_unequal_feature_dims_in_chunk_mode(cuda_lib):
+    """d != e with few (batch, head) pairs: the three products of the backward pass plan different chunk counts and the
+    workspace must cover the largest (lab200_la2_bwd_workspace_bytes)."""
+    for (b, h, n, d, e) in ((1, 32, 2048, 128, 256), (1, 32, 2048, 64, 192)):
+        q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 1.0, seed=5)
+        s = la._build_slope_tensor(h).to(DEV)
+        got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn2(a, b_, c, s), q, k, v, do)
+        compare_with_torch_reference(q, k, v, do, s, got, False, f"unequal-dims{(d, e)}")
+
+
+def test_interface_splits_wide_value_dims(cuda_lib):
+    """e > 256 through lightning_attn_func: column slices of v, forward and backward (the reference pads e to a power of
+    two instead, lightning_attn_interface.py:28-32)."""
+    b, h, n, d, e = 1, 2, 384, 64, 320
+    q, k, v, do = make_inputs(b, h, n, d, e, torch.bfloat16, 1.0, seed=6)
+    s = la._build_slope_tensor(h).to(DEV)
+    got = run_fwd_bwd(lambda a, b_, c: la.lightning_attn_func(a, b_, c, s), q, k, v, do)
+    assert got[0].shape == (b, h, n, e)
+    compare_with_torch_reference(q, k, v, do, s, got, False, "wide-e")
+
+
+def test_fp32_inputs_are_refused_with_a_clear_message(cuda_lib):
+    q = torch.randn(1, 2, 128, 64, device=DEV)
+    with pytest.raises(RuntimeError, match="bf16 or fp16"):
+        la.lightning_attn2(q, q, q, la._build_slope_tensor(2).to(DEV))
+
+
+def test_expired_device_wait_reaches_the_caller_one_call_late(cuda_lib):
+    """The bounded waits of the block kernels end in an error word, not a hang. Here a tiny kernel lets such a wait run out
+    on purpose (a barrier nothing arrives on, 1e5-cycle budget, no copies or MMAs in flight); the word must show up in the
+    workspace, then through lab200_last_status, and the next operator call must raise - after which the device is usable."""
+    ws = torch.zeros(256, dtype=torch.uint8, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    assert cuda_lib.lab200_last_status() == 0
+    assert cuda_lib.lab200_debug_wait_expiry(ws.data_ptr(), 256, 100000, stream) == 0
+    assert cuda_lib.lab200_read_status(ws.data_ptr(), stream) == 101  # synchronises
+    torch.cuda.synchronize()
+    q, k, v, _ = make_inputs(1, 2, 256, 64, 64, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(2).to(DEV)
+    with pytest.raises(RuntimeError, match="earlier lightning attention call"):
+        la.lightning_attn2(q, k, v, s)
+    assert cuda_lib.lab200_last_status() == 0  # reported once
+    o = la.lightning_attn2(q, k, v, s)  # the context is intact
+    torch.cuda.synchronize()
+    assert torch.isfinite(o.float()).all()
+    assert cuda_lib.lab200_last_status() == 0

@@ -43,7 +43,23 @@ def oracle_product(a, bm, c, s=None, reverse=False, state_in=None, want_state=Fa
     return out_t, st_t
 
 
-def _sp_worker(rank, world, port, scale, result_dir, d=16, e=32):
+def oracle_dkdv(q, k, v, s, do, state_in=None, chunks=0, resume_from=None):
+    """Same call signature as the CUDA op `la_dkdv` (fused dk + dv sweep), computed by the numpy oracle as the two
+    reverse-time products it fuses; state_in is the (b, h, d, e) reverse-time state, and a handle must come from a
+    state-only reverse-time call on (do, q) that has not had an incoming state added yet."""
+    from oracle import lightning_oracle as O
+
+    f = lambda t: None if t is None else t.detach().double().numpy()
+    if resume_from is not None:
+        tag, bshape, cshape, rev, based = resume_from
+        assert (tag, bshape, cshape, rev, based) == ("handle", tuple(do.shape), tuple(q.shape), True, False)
+    st = f(state_in)
+    dk, _ = O.la_generic(f(v), f(do), f(q), f(s), reverse=True, state_in=st)
+    dv, _ = O.la_generic(f(k), f(q), f(do), f(s), reverse=True, state_in=None if st is None else np.swapaxes(st, -1, -2))
+    return torch.from_numpy(np.ascontiguousarray(dk)), torch.from_numpy(np.ascontiguousarray(dv))
+
+
+def _sp_worker(rank, world, port, scale, result_dir, d=16, e=32, fused=False):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -60,7 +76,7 @@ def _sp_worker(rank, world, port, scale, result_dir, d=16, e=32):
         s = None if scale == 0 else torch.from_numpy(O.build_slopes(h)).double().reshape(h, 1, 1) * scale
         sl = slice(rank * L, (rank + 1) * L)
         ql, kl, vl = (t[:, :, sl].clone().requires_grad_() for t in (q, k, v))
-        o = D.lightning_attn_sp(ql, kl, vl, s, product=oracle_product)
+        o = D.lightning_attn_sp(ql, kl, vl, s, product=oracle_product, dkdv=oracle_dkdv if fused else None)
         o.backward(do[:, :, sl])
         sn = None if s is None else s.numpy()
         ro = O.linear_attn(q.numpy(), k.numpy(), v.numpy(), sn)
@@ -89,6 +105,17 @@ def test_sequence_parallel_square_dims_reuse_transposed_states(tmp_path):
     the product stand-in checks every handle it is given (right product, incoming state added exactly once)."""
     world = 2
     mp.spawn(_sp_worker, args=(world, _free_port(), 1e-3, str(tmp_path), 32, 32), nprocs=world, join=True)
+    for r in range(world):
+        errs = np.load(tmp_path / f"err_{r}.npy")
+        assert np.all(errs < 1e-4), (r, errs)
+
+
+@pytest.mark.parametrize("scale", [1e-3, 0.0])
+def test_sequence_parallel_with_the_fused_dk_dv_sweep(tmp_path, scale):
+    """The backward branch the CUDA path takes for d, e <= 128: one state-only pass over (do, q), the exchange, then ONE
+    fused call for dk and dv that takes the combined incoming state and the kept handle."""
+    world = 2
+    mp.spawn(_sp_worker, args=(world, _free_port(), scale, str(tmp_path), 16, 32, True), nprocs=world, join=True)
     for r in range(world):
         errs = np.load(tmp_path / f"err_{r}.npy")
         assert np.all(errs < 1e-4), (r, errs)

@@ -135,3 +135,45 @@ def test_torch_srmsnorm_matches_reference(golden_dir):
     y.backward(torch.from_numpy(g["dy"]))
     np.testing.assert_allclose(y.detach().numpy(), g["y"], rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(x.grad.numpy(), g["dx"], rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["attn_c1_fp32_sum", "attn_ragged_fp32", "attn_nodecay_fp32"])
+@pytest.mark.parametrize("block", [64, 256])
+def test_gpu_side_torch_reference_is_pinned_to_the_reference(golden_dir, name, block):
+    """tests/_refs.py:torch_la_reference - the fp32 torch block recurrence most GPU parity tests compare with - reproduces
+    the reference's outputs and autograd gradients on the golden fixtures (ragged n and non-power-of-two head counts
+    included) and agrees with the numpy oracle; run here on the CPU, it is the same code the GPU tests run on the device."""
+    import sys
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _refs import torch_la_reference
+    from oracle import lightning_oracle as O
+
+    g = dict(np.load(os.path.join(golden_dir, name + ".npz")))
+    q, k, v, do = (torch.from_numpy(g[x]).requires_grad_() for x in ("q", "k", "v", "do"))
+    s = torch.from_numpy(g["s"]).reshape(-1, 1, 1) if "s" in g else None
+    o = torch_la_reference(q, k, v, s, block=block)
+    o.backward(do.detach())
+    odq, odk, odv = O.linear_attn_bwd(g["q"], g["k"], g["v"], g.get("s"), g["do"])
+    oo = O.linear_attn(g["q"], g["k"], g["v"], g.get("s"))
+    for got, key, orc in ((o, "o", oo), (q.grad, "dq", odq), (k.grad, "dk", odk), (v.grad, "dv", odv)):
+        got = got.detach().numpy()
+        assert O.rel_l2_err(got, g[key]) < 5e-6, (key, "vs the reference fixture")
+        assert O.rel_l2_err(got, orc) < 5e-6, (key, "vs the numpy oracle")
+
+
+def test_backward_workspace_covers_every_product_of_the_backward_pass():
+    """lab200_la2_bwd runs products with (dk, dv) = (e, d) and (d, e); each plans its own chunks, and the size the Python
+    layer asks for must cover the largest (d != e with few (batch, head) pairs used to come out too small)."""
+    L = _lib.lib()
+    for (b, h, n, d, e) in ((1, 32, 2048, 128, 256), (1, 32, 4096, 128, 192), (1, 48, 2048, 192, 64), (1, 40, 2048, 64, 192),
+                            (4, 32, 32768, 128, 128), (1, 4, 131072, 128, 128)):
+        need = L.lab200_la2_bwd_workspace_bytes(b, h, n, d, e, 0)
+        assert need >= L.lab200_la_workspace_bytes(b * h, n, e, d, 0)
+        assert need >= L.lab200_la_workspace_bytes(b * h, n, d, e, 0)
+        assert need >= 256
+
+
+def test_status_queries_need_no_gpu():
+    L = _lib.lib()
+    assert L.lab200_last_status() == 0  # no device, no ring: nothing to report

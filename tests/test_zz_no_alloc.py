@@ -59,8 +59,23 @@ def test_static_scratch_entry_point_matches_regular_one_twice(cuda_lib):
     for seed in (1, 2):  # two calls in a row on the same array, different data
         q, k, v, s = _inputs(seed, b, h, n, d, e)
         want = _regular(L, q, k, v, s, chunks)
+        o_static = torch.empty((b, h, n, e), dtype=q.dtype, device=DEV)
+        stream = torch.cuda.current_stream().cuda_stream
+        L.lab200_la2_fwd_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), s.data_ptr(), o_static.data_ptr(), b, h, n, d, e,
+                                chunks, _lib.BF16, stream)  # first call on the device looks up the array's address
+        torch.cuda.synchronize()
+        # the call itself takes no device memory: neither from the driver nor from torch's caching allocator
+        free0, reserved0, allocated0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved(), torch.cuda.memory_allocated()
+        rc = L.lab200_la2_fwd_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), s.data_ptr(), o_static.data_ptr(), b, h, n, d, e,
+                                     chunks, _lib.BF16, stream)
+        torch.cuda.synchronize()
+        assert rc == 0
+        assert torch.cuda.mem_get_info()[0] == free0
+        assert torch.cuda.memory_reserved() == reserved0 and torch.cuda.memory_allocated() == allocated0
+        assert L.lab200_static_status(stream) == 0  # the status word of the built-in array: no bounded wait ran out
         got = _static(L, q, k, v, s, chunks)
         torch.cuda.synchronize()
+        assert torch.equal(got, o_static)
         assert torch.isfinite(got.float()).all()
         assert _rel_l2(got, want) <= 1e-2  # the tolerance of the other attention tests; in practice the two agree bit for bit
         assert float((got.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
