@@ -763,7 +763,7 @@ def cpu_reference_naive():
         o.sum().backward()
         t2 = time.perf_counter()
         out["attention"].append({"config": tag, "shape": [b, h, n, d, d], "fwd_s": t1 - t0, "bwd_s": t2 - t1,
-                                 "tokens_per_s": scale_b * b * n / (t2 - t0) / scale_b if scale_b == 1 else b * n / (t2 - t0),
+                                 "tokens_per_s": b * n / (t2 - t0),  # the same for the whole config: time and tokens both scale with b
                                  "batch_entries_timed": b, "batch_entries_in_config": b * scale_b})
 
     attn(1, 4, 256, 64, "config 1")

@@ -338,17 +338,17 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
 
 // ---- fused dk + dv (one reverse sweep) -----------------------------------------------------------------
 int smem_bytes_dkdv(int ne) {
-  return 12 * LA_SLAB_BYTES + ne * LA_SLAB_BYTES + 2 * LD2_NUM_BARS * 8 + 16 + 512 + 1024;
+  return 12 * LA_SLAB_BYTES + ne * LA_SLAB_BYTES + 2 * LD2_NUM_BARS * 8 + 16 + 512 + 1024;  // q 2, do 4, k 2, v 2, staging 2, state copy ne
 }
 
 template <int ND, int NE, int FMT>
-int launch_dkdv_one(const CUtensorMap (&tm)[4], const LaDkdvParams& p, dim3 grid, int smem, cudaStream_t st) {
+int launch_dkdv_one(const CUtensorMap (&tm)[6], const LaDkdvParams& p, dim3 grid, int smem, cudaStream_t st) {
   auto kern = la_dkdv2_kernel<ND, NE, FMT>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     cudaGetLastError();
     return LAB200_ERR_CUDA;
   }
-  kern<<<grid, LAP_THREADS, smem, st>>>(tm[0], tm[1], tm[2], tm[3], p);
+  kern<<<grid, LAP_THREADS, smem, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
 }
@@ -377,18 +377,18 @@ int la_dkdv_impl(const void* q, const void* k, const void* v, const void* dout, 
   const int nd = (d + 63) / 64, ne = (e + 63) / 64;
   const int smem = smem_bytes_dkdv(ne);
   if (smem > SMEM_LIMIT) return LAB200_ERR_SHAPE;
-  CUtensorMap tm[4];
+  CUtensorMap tm[6];
   int rc;
   if ((rc = make_tmap(&tm[0], q, bh, n, d, dtype, layout, h)) != LAB200_OK) return rc;
   if ((rc = make_tmap(&tm[1], k, bh, n, d, dtype, layout, h)) != LAB200_OK) return rc;
   if ((rc = make_tmap(&tm[2], v, bh, n, e, dtype, layout, h)) != LAB200_OK) return rc;
   if ((rc = make_tmap(&tm[3], dout, bh, n, e, dtype, layout, h)) != LAB200_OK) return rc;
+  if ((rc = make_tmap(&tm[4], dk, bh, n, d, dtype, layout, h)) != LAB200_OK) return rc;  // the output tiles leave through TMA stores
+  if ((rc = make_tmap(&tm[5], dv, bh, n, e, dtype, layout, h)) != LAB200_OK) return rc;
   LaDkdvParams p;
   p.slopes = slopes;
   p.state_in = states;
   p.state_out = nullptr;
-  p.dk_out = dk;
-  p.dv_out = dv;
   p.status = static_cast<int*>(workspace);
   p.n = n; p.h = h; p.d = d; p.e = e;
   p.nblocks = (n + LA_BLOCK - 1) / LA_BLOCK;

@@ -16,8 +16,10 @@
 //                                                                                    term is a second K range of the same
 //                                                                                    tcgen05.mma chain, A read from TMEM)
 //   D  = (lambda^r q)^T do ;  dKV <- lambda^128 dKV + D                             (fp32 registers + bf16 copy in smem)
-// The output rows go from TMEM through registers straight to global memory (32-byte stores), which frees the k and v
-// buffers as soon as their S product and scaled copy are done: k and v are single-buffered, q and do double-buffered.
+// Shared memory: do double-buffered; q, k, v single-buffered (k and v are free as soon as their S product and scaled copy
+// are done; q is free once D, issued right after the dk half, has read it); one 32 KB staging buffer through which the dk
+// tile and then the dv tile of a block leave by TMA store (row-per-thread stores straight from registers to global
+// memory were measured 1500 cycles per block slower: 32 distinct lines per warp instruction).
 //
 // Roles: warp 0 TMA producer, warp 1 MMA issuer (one thread), warps 2-5 mask group (one per TMEM lane quadrant),
 // warps 6-13 state/output group. Every wait is bounded and polls a CTA-wide abort flag.
@@ -32,8 +34,6 @@ struct LaDkdvParams {
   const float* slopes;     // [h] decay rates or nullptr
   const float* state_in;   // [bh][state_slots][d][e] fp32 reverse-time state entering the (chunk of the) sequence, or nullptr
   float* state_out;        // same indexing, or nullptr
-  void* dk_out;            // [bh][n][d] (or (b, n, h, d) with layout = 1), input dtype
-  void* dv_out;            // [bh][n][e]
   int* status;
   int n, h, d, e;
   int nblocks, blocks_per_chunk, chunk0, state_slots;
@@ -45,16 +45,17 @@ struct LaDkdvParams {
 
 // barrier slots; every slot has two instances indexed by block parity
 enum : int {
-  LD2_FULL_QG = 0, LD2_FULL_V, LD2_FULL_K,
+  LD2_FULL_Q = 0, LD2_FULL_G, LD2_FULL_V, LD2_FULL_K,
   LD2_S0_READY, LD2_S1_READY, LD2_P0_READY, LD2_P1_READY, LD2_VS_READY, LD2_KS_READY,
-  LD2_PC0_DONE, LD2_PC1_DONE, LD2_O_FREE0, LD2_O_FREE1,
+  LD2_PC0_DONE, LD2_PC1_DONE, LD2_O_FREE0, LD2_O_FREE1, LD2_O_STAGED0, LD2_O_STAGED1, LD2_BUF_FREE0, LD2_BUF_FREE1,
   LD2_Q_SCALED, LD2_D_DONE, LD2_D_FREE, LD2_STATE_READY, LD2_NUM_BARS
 };
 
 template <int ND, int NE, int FMT>
 __global__ void __launch_bounds__(LAP_THREADS, 1)
 la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG, const LaDkdvParams p) {
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
+                const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV, const LaDkdvParams p) {
   static_assert(ND <= 2 && NE <= 2, "d, e <= 128");
   constexpr int SLAB = LA_SLAB_BYTES;
   constexpr int DQ = 64 * ND, DE = 64 * NE;
@@ -71,11 +72,12 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t sQ = base;                 // 2 stages x 2 slabs
-  const uint32_t sG = sQ + 4 * SLAB;        // 2 stages x 2 slabs
+  const uint32_t sQ = base;                 // 2 slabs
+  const uint32_t sG = sQ + 2 * SLAB;        // 2 stages x 2 slabs
   const uint32_t sK = sG + 4 * SLAB;        // 2 slabs
   const uint32_t sV = sK + 2 * SLAB;        // 2 slabs
-  const uint32_t sS = sV + 2 * SLAB;        // bf16 copy of dKV: NE slabs of [128 rows (d)][64 columns (e)]
+  const uint32_t sO = sV + 2 * SLAB;        // 2 slabs: staging of the dk tile, then of the dv tile
+  const uint32_t sS = sO + 2 * SLAB;        // bf16 copy of dKV: NE slabs of [128 rows (d)][64 columns (e)]
   const uint32_t sBar = sS + NE * SLAB;
   const uint32_t sMisc = sBar + 2 * LD2_NUM_BARS * 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sMisc - raw));
@@ -106,7 +108,7 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t count = 1u;
       if (i == LD2_P0_READY || i == LD2_P1_READY) count = LAP_MASK_THREADS;
       if (i == LD2_VS_READY || i == LD2_KS_READY || i == LD2_O_FREE0 || i == LD2_O_FREE1 || i == LD2_Q_SCALED ||
-          i == LD2_D_FREE || i == LD2_STATE_READY)
+          i == LD2_D_FREE || i == LD2_STATE_READY || i == LD2_O_STAGED0 || i == LD2_O_STAGED1)
         count = LAP_STATE_THREADS;
       mbar_init(sBar + (i * 2) * 8, count);
       mbar_init(sBar + (i * 2 + 1) * 8, count);
@@ -115,6 +117,7 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     *fail_code = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmG);
+    tma_prefetch_desc(&tmDK); tma_prefetch_desc(&tmDV);
   }
   if (tid < LA_BLOCK) decay_tab[tid] = ex2f(s2 * static_cast<float>(tid));
   if (warp == 0) {
@@ -133,33 +136,60 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (warp == 0) {
     // =========================================== TMA producer ===========================================
+    // Loads of block it are issued as their buffers come free during block it-1; in between, the two staged output tiles of
+    // block it-1 are stored. The order below is the order in which these events happen in a block.
     if (lane == 0) {
+      auto store_tile = [&](int i, int u) -> bool {  // tile u (0: dk, 1: dv) of block i: staged -> global, then free the buffer
+        if (!lap_wait(bar(u ? LD2_O_STAGED1 : LD2_O_STAGED0, i), par(i), abort_flag, budget)) return false;
+        const int nslab = u ? NE : ND;
+        for (int sl = 0; sl < nslab; ++sl)
+          tma_store_3d(u ? static_cast<const void*>(&tmDV) : static_cast<const void*>(&tmDK), sO + sl * SLAB, sl * 64,
+                       blk_of(i) * LA_BLOCK, zc);
+        tma_store_commit();
+        tma_store_wait_read();
+        mbar_arrive(bar(u ? LD2_BUF_FREE1 : LD2_BUF_FREE0, i));
+        return true;
+      };
+      bool alive = true;
       for (int it = 0; it < nb; ++it) {
         const int blk = blk_of(it);
         const int st = it & 1;
-        if (it >= 2) { LD2_WAIT(LD2_D_DONE, it - 2, LA_ERR_WAIT_MMA2) }  // D of block it-2 was the last reader of this q, do stage
-        mbar_arrive_expect_tx(bar(LD2_FULL_QG, it), (2 + NE) * SLAB);
-        for (int sl = 0; sl < 2; ++sl)  // q always as two slabs: it is the M = 128 side of the state MMA
-          tma_load_3d(sQ + (st * 2 + sl) * SLAB, &tmQ, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_QG, it));
+        alive = false;
+        // do: P1 do of block it-2 was the last reader of this stage
+        if (it >= 2) { LD2_WAIT(LD2_PC1_DONE, it - 2, LA_ERR_WAIT_MMA2) }
+        mbar_arrive_expect_tx(bar(LD2_FULL_G, it), NE * SLAB);
         for (int sl = 0; sl < NE; ++sl)
-          tma_load_3d(sG + (st * 2 + sl) * SLAB, &tmG, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_QG, it));
+          tma_load_3d(sG + (st * 2 + sl) * SLAB, &tmG, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_G, it));
         // v of the previous block: S0 has consumed it (P0 exists) and its scaled copy sits in TMEM
         if (it >= 1) { LD2_WAIT(LD2_VS_READY, it - 1, LA_ERR_WAIT_MMA1) }
         mbar_arrive_expect_tx(bar(LD2_FULL_V, it), NE * SLAB);
         for (int sl = 0; sl < NE; ++sl) tma_load_3d(sV + sl * SLAB, &tmV, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_V, it));
+        if (it >= 1 && !store_tile(it - 1, 0)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
+        // q of the previous block: D was its last reader
+        if (it >= 1) { LD2_WAIT(LD2_D_DONE, it - 1, LA_ERR_WAIT_MMA2) }
+        mbar_arrive_expect_tx(bar(LD2_FULL_Q, it), 2 * SLAB);
+        for (int sl = 0; sl < 2; ++sl)  // q always as two slabs: it is the M = 128 side of the state MMA
+          tma_load_3d(sQ + sl * SLAB, &tmQ, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_Q, it));
         if (it >= 1) { LD2_WAIT(LD2_KS_READY, it - 1, LA_ERR_WAIT_MMA1) }
         mbar_arrive_expect_tx(bar(LD2_FULL_K, it), ND * SLAB);
         for (int sl = 0; sl < ND; ++sl) tma_load_3d(sK + sl * SLAB, &tmK, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_K, it));
+        if (it >= 1 && !store_tile(it - 1, 1)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
+        alive = true;
       }
+      if (alive && nb > 0 && *abort_flag == 0) {
+        if (!store_tile(nb - 1, 0) || !store_tile(nb - 1, 1)) LD2_FAIL(LA_ERR_WAIT_MMA2)
+      }
+      tma_store_wait_all();
     }
   } else if (warp == 1) {
     // ============================================ MMA issuer ============================================
-    // Issue order per block: [P0 q, Vs dKV^T] -> dk; S0 of the next block; [P1 do, Ks dKV] -> dv; S1 of the next block;
-    // D. The two S products of block it+1 are in TMEM long before the mask group gets to them.
+    // Issue order per block: [P0 q, Vs dKV^T] -> dk; S0 of the next block; D (the last reader of q, whose buffer is then
+    // reloaded); [P1 do, Ks dKV] -> dv; S1 of the next block. The two S products of block it+1 are in TMEM before the mask
+    // group gets to them.
     if (lane == 0) {
       auto issue_S0 = [&](int i) -> bool {  // S0 = v do^T (contraction over e)
         if (!lap_wait(bar(LD2_FULL_V, i), par(i), abort_flag, budget)) return false;
-        if (!lap_wait(bar(LD2_FULL_QG, i), par(i), abort_flag, budget)) return false;
+        if (!lap_wait(bar(LD2_FULL_G, i), par(i), abort_flag, budget)) return false;
         tc_fence_after_sync();
         const uint32_t g0 = sG + (i & 1) * 2 * SLAB;
         for (int kq = 0; kq < ne16; ++kq) {
@@ -171,9 +201,9 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
       auto issue_S1 = [&](int i) -> bool {  // S1 = k q^T (contraction over d)
         if (!lap_wait(bar(LD2_FULL_K, i), par(i), abort_flag, budget)) return false;
-        if (!lap_wait(bar(LD2_FULL_QG, i), par(i), abort_flag, budget)) return false;
+        if (!lap_wait(bar(LD2_FULL_Q, i), par(i), abort_flag, budget)) return false;
         tc_fence_after_sync();
-        const uint32_t q0 = sQ + (i & 1) * 2 * SLAB;
+        const uint32_t q0 = sQ;
         for (int kq = 0; kq < nd16; ++kq) {
           const uint32_t off = (kq >> 2) * SLAB + (kq & 3) * 32;
           umma_f16(tmem + T_SB, smem_desc_sw128(sK + off, 16), smem_desc_sw128(q0 + off, 16), IDESC_S, kq > 0);
@@ -187,7 +217,7 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!alive) LD2_FAIL(LA_ERR_WAIT_INPUT)
       }
       for (int it = 0; it < nb && alive; ++it) {
-        const uint32_t sQs = sQ + (it & 1) * 2 * SLAB, sGs = sG + (it & 1) * 2 * SLAB;
+        const uint32_t sQs = sQ, sGs = sG + (it & 1) * 2 * SLAB;
         const bool have_state = have_state_in || (it > 0);
         LD2_TRACE(0, it)
         // ---- dk = P0 q + Vs dKV^T -------------------------------------------------------------------------------
@@ -213,6 +243,15 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!issue_S0(it + 1)) { LD2_FAIL(LA_ERR_WAIT_INPUT) break; }
         }
         LD2_TRACE(3, it)
+        // ---- D = (w_state q)^T do ------------------------------------------------------------------------------
+        LD2_WAIT(LD2_Q_SCALED, it, LA_ERR_WAIT_MMA2)
+        if (it > 0) { LD2_WAIT(LD2_D_FREE, it - 1, LA_ERR_WAIT_MMA2) }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem + T_D, smem_desc_sw128(sQs + kk * 2048, SLAB), smem_desc_sw128(sGs + kk * 2048, SLAB), IDESC_D, kk > 0);
+        umma_commit(bar(LD2_D_DONE, it));
+        LD2_TRACE(7, it)
         // ---- dv = P1 do + Ks dKV -----------------------------------------------------------------------------------
         LD2_WAIT(LD2_P1_READY, it, LA_ERR_WAIT_MMA1)
         LD2_WAIT(LD2_O_FREE0, it, LA_ERR_WAIT_MMA2)  // the dk epilogue has read O
@@ -233,15 +272,6 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!issue_S1(it + 1)) { LD2_FAIL(LA_ERR_WAIT_INPUT) break; }
         }
         LD2_TRACE(6, it)
-        // ---- D = (w_state q)^T do ------------------------------------------------------------------------------
-        LD2_WAIT(LD2_Q_SCALED, it, LA_ERR_WAIT_MMA2)
-        if (it > 0) { LD2_WAIT(LD2_D_FREE, it - 1, LA_ERR_WAIT_MMA2) }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem + T_D, smem_desc_sw128(sQs + kk * 2048, SLAB), smem_desc_sw128(sGs + kk * 2048, SLAB), IDESC_D, kk > 0);
-        umma_commit(bar(LD2_D_DONE, it));
-        LD2_TRACE(7, it)
       }
     }
   } else if (warp < 6) {
@@ -327,8 +357,6 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float decay_blk = ex2f(s2 * static_cast<float>(LA_BLOCK));
     const bool st_row_valid = (r < p.d);
     const bool tracer = (w8 == 0 && lane == 0);
-    const bool wide_dk = (reinterpret_cast<uintptr_t>(p.dk_out) & 31u) == 0;
-    const bool wide_dv = (reinterpret_cast<uintptr_t>(p.dv_out) & 31u) == 0;
 
     float stt[SC];  // dKV[r][hf * SC ...]
 #pragma unroll
@@ -383,20 +411,17 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
     };
 
-    // epilogue of half U: O -> registers -> global rows of dk (U = 0) or dv (U = 1)
+    // epilogue of half U: O -> registers -> swizzled tile in the staging buffer (dk for U = 0, dv for U = 1); the producer
+    // warp stores it. The buffer is free once the previous tile (the other half) has been read by its TMA store.
     auto epilogue = [&](auto u_tag, int it) -> bool {
       constexpr int U = decltype(u_tag)::value;
       constexpr int OC = (U == 0 ? DQ : DE) / 2;
       bool ok = lap_wait(bar(U ? LD2_PC1_DONE : LD2_PC0_DONE, it), par(it), abort_flag, budget);
+      if (U == 1) ok = ok && lap_wait(bar(LD2_BUF_FREE0, it), par(it), abort_flag, budget);
+      if (U == 0 && it > 0) ok = ok && lap_wait(bar(LD2_BUF_FREE1, it - 1), par(it - 1), abort_flag, budget);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) return false;
       tc_fence_after_sync();
-      const int dim = U ? p.e : p.d;
-      const int tok = blk_of(it) * LA_BLOCK + r;
-      const size_t row_index = p.layout ? (static_cast<size_t>(bh / p.h) * p.n + tok) * p.h + (bh % p.h)
-                                        : static_cast<size_t>(bh) * p.n + tok;
-      uint8_t* out_row = static_cast<uint8_t*>(U ? p.dv_out : p.dk_out) + row_index * dim * 2;
-      const bool wide = U ? wide_dv : wide_dk;
 #pragma unroll
       for (int cc = 0; cc < OC; cc += 16) {
         uint32_t a[16];
@@ -406,18 +431,23 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_before_sync();
           mbar_arrive(bar(U ? LD2_O_FREE1 : LD2_O_FREE0, it));
         }
-        uint32_t o8[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o8[j] = pack2<FMT>(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1]));
-        const int col = hf * OC + cc;
-        if (tok < p.n && col < dim) st_global_row32(out_row + col * 2, o8, wide);
+        for (int g = 0; g < 2; ++g) {
+          const int col = hf * OC + cc + g * 8;
+          st_shared_v4(sO + (col >> 6) * SLAB + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4),
+                       pack2<FMT>(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1])),
+                       pack2<FMT>(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3])),
+                       pack2<FMT>(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5])),
+                       pack2<FMT>(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7])));
+        }
       }
+      fence_proxy_async_smem();
+      mbar_arrive(bar(U ? LD2_O_STAGED1 : LD2_O_STAGED0, it));
       return true;
     };
 
     for (int it = 0; it < nb; ++it) {
       const bool has_next = (it + 1 < nb);
-      const uint32_t sQs = sQ + (it & 1) * 2 * SLAB;
       // ---- Vs = w v into SA[64, 128): the mask group is done with S0 ----------------------------------------------
       {
         bool ok = lap_wait(bar(LD2_P0_READY, it), par(it), abort_flag, budget);
@@ -428,7 +458,7 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive(bar(LD2_VS_READY, it));
         if (tracer) { LD2_TRACE(12, it) }
       }
-      // ---- dk rows ---------------------------------------------------------------------------------------------
+      // ---- dk tile ---------------------------------------------------------------------------------------------
       if (!epilogue(std::integral_constant<int, 0>{}, it)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
       if (tracer) { LD2_TRACE(13, it) }
       // ---- q rows *= w_state(r), in place, for D: S1 and P0 q are done with the unscaled tile -------------------------
@@ -445,7 +475,7 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int gch = hf * NCH + c;
             const int ks = gch >> 3, p0 = gch & 7;
             const int pos = (NCH >= 8) ? ((p0 + r) & 7) : ((p0 & 4) | ((p0 + r) & 3));
-            addr[c] = sQs + ks * SLAB + r * 128 + (pos << 4);
+            addr[c] = sQ + ks * SLAB + r * 128 + (pos << 4);
             ld_shared_v4(addr[c], u[c][0], u[c][1], u[c][2], u[c][3]);
           }
 #pragma unroll
@@ -468,9 +498,7 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive(bar(LD2_KS_READY, it));
         if (tracer) { LD2_TRACE(14, it) }
       }
-      // ---- dv rows ---------------------------------------------------------------------------------------------
-      if (!epilogue(std::integral_constant<int, 1>{}, it)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
-      // ---- state recurrence: dKV = lambda^128 dKV + D ---------------------------------------------------------------
+      // ---- state recurrence: dKV = lambda^128 dKV + D (registers; the shared-memory copy follows the dv half) ---------
       {
         bool ok = lap_wait(bar(LD2_D_DONE, it), par(it), abort_flag, budget);
         ok = __all_sync(0xffffffffu, ok);
@@ -487,7 +515,9 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_before_sync();
       mbar_arrive(bar(LD2_D_FREE, it));
-      if (has_next) {  // D_DONE follows both halves of this block in the tensor pipe: they are done with the old copy
+      // ---- dv tile ---------------------------------------------------------------------------------------------
+      if (!epilogue(std::integral_constant<int, 1>{}, it)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
+      if (has_next) {  // PC1_DONE (awaited by the dv epilogue) covers both halves of this block: they are done with the old copy
         store_state_smem();
         fence_proxy_async_smem();
         mbar_arrive(bar(LD2_STATE_READY, it + 1));

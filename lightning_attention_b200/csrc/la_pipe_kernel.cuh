@@ -19,10 +19,6 @@
 
 namespace lab200 {
 
-#ifndef LAP_DIRECT_STORE
-#define LAP_DIRECT_STORE 0  // 1: output rows go from registers straight to global memory; 0: staged in shared memory + TMA store
-#endif
-
 constexpr int LAP_THREADS = 448;
 constexpr int LAP_MASK_THREADS = 128, LAP_STATE_THREADS = 256;
 
@@ -49,18 +45,6 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-// 32 bytes (16 output elements) of one row, registers -> global; `wide` = the address is 32-byte aligned
-__device__ __forceinline__ void st_global_row32(void* dst, const uint32_t (&o)[8], bool wide) {
-  if (wide) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]),
-                 "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
-  } else {
-    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(static_cast<uint8_t*>(dst) + 16), "r"(o[4]), "r"(o[5]),
-                 "r"(o[6]), "r"(o[7]) : "memory");
-  }
-}
 
 // Bounded, abortable wait. Returns false if the budget ran out here or another role gave up.
 __device__ __forceinline__ bool lap_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, long long budget) {
@@ -180,14 +164,9 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t prev_par = ((it >> 1) & 1) ^ 1;  // parity of the previous use of this stage (block it-2)
         if (MODE == 0) {
           if (it >= 2) {
-#if LAP_DIRECT_STORE
-            // P C of block it-2 was the last MMA to touch that block's A, Bm and C
-            if (!lap_wait(bar(LAP_PC_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
-#else
             // A staged output tile means P C of block it-2 has run, the last MMA to touch that block's A, Bm and C.
             // The A stage holds the tile: store it; Bm and C can be reloaded at once, A when the store has read the tile.
             if (!store_tile(it - 2)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
-#endif
           }
         } else if (it >= 2) {
           if (!lap_wait(bar(LAP_D_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
@@ -200,25 +179,19 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int vs = 0; vs < 2; ++vs)
           tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_BC, st));
         if (MODE == 0) {
-#if !LAP_DIRECT_STORE
           if (it >= 2) tma_store_wait_read();
-#endif
           mbar_arrive_expect_tx(bar(LAP_FULL_A, st), NKS * SLAB);
 #pragma unroll
           for (int ks = 0; ks < NKS; ++ks)
             tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_A, st));
         }
       }
-#if !LAP_DIRECT_STORE
       if (MODE == 0 && alive && *abort_flag == 0) {
         for (int i = max(nb - 2, 0); i < nb; ++i) {
           if (!store_tile(i)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         }
       }
       if (MODE == 0) tma_store_wait_all();
-#else
-      (void)store_tile;
-#endif
     }
   } else if (warp == 1) {
     // ============================================ MMA issuer ============================================
@@ -386,8 +359,6 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const float decay_tail = ex2f(s2 * static_cast<float>(tail));
     const bool st_row_valid = (r < DV) && (dv_off + r < p.dv);
     const bool store_thread = (w8 == 0 && lane == 0);
-    // 32-byte stores need a 32-byte aligned base; rows are dv * 2 bytes apart, dv a multiple of 16 (CTA-uniform)
-    const bool out_wide = (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0;
 
     float stt[SC];
 #pragma unroll
@@ -504,17 +475,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         if (store_thread) { LAP_TRACE(7, it) }
         tc_fence_after_sync();
-#if LAP_DIRECT_STORE
-        const int blk_o = reverse ? (blk_end - 1 - it) : (blk_begin + it);
-        const int tok = blk_o * LA_BLOCK + r;
-        const bool row_ok = tok < p.n;
-        // row of this token in the output tensor: (bh, n, dv) or, with the projection layout, (b, n, h, dv)
-        const size_t row_index = p.layout ? (static_cast<size_t>(bh / p.h) * p.n + tok) * p.h + (bh % p.h)
-                                          : static_cast<size_t>(bh) * p.n + tok;
-        uint8_t* out_row = static_cast<uint8_t*>(p.out) + row_index * p.dv * 2;
-#else
         const uint32_t sOs = sA + st * NAS * SLAB;  // S_it and X_it are done with this A stage
-#endif
 #pragma unroll
         for (int cc = 0; cc < OC; cc += 16) {
           uint32_t a[16], b[16];
@@ -526,22 +487,6 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_arrive(bar(LAP_O_FREE, st));
             if (store_thread) { LAP_TRACE(10, it) }
           }
-#if LAP_DIRECT_STORE
-          {
-            uint32_t o8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float x0 = __uint_as_float(a[2 * j]), x1 = __uint_as_float(a[2 * j + 1]);
-              if (have_state) {
-                x0 = fmaf(w_out, __uint_as_float(b[2 * j]), x0);
-                x1 = fmaf(w_out, __uint_as_float(b[2 * j + 1]), x1);
-              }
-              o8[j] = pack2<FMT>(x0, x1);
-            }
-            const int col = dv_off + hf * OC + cc;  // 16 columns of this row; dv is a multiple of 16
-            if (row_ok && col < p.dv) st_global_row32(out_row + col * 2, o8, out_wide);
-          }
-#else
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
             uint32_t o4[4];
@@ -557,12 +502,9 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int col = hf * OC + cc + g * 8;  // column inside this CTA's dv slice
             st_shared_v4(sOs + (col >> 6) * SLAB + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4), o4[0], o4[1], o4[2], o4[3]);
           }
-#endif
         }
-#if !LAP_DIRECT_STORE
         fence_proxy_async_smem();
         mbar_arrive(bar(LAP_O_STAGED, st));  // the producer warp stores the tile
-#endif
         if (store_thread) { LAP_TRACE(11, it) }
       }
       if (MODE == 0 && has_next && !scale_bm(it + 1)) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
