@@ -427,17 +427,22 @@ def leg_config2(torch, la, dev, hbm_peak):
     q, k, v = (torch.randn((b, h, n, d), device=dev, generator=g).to(torch.bfloat16).requires_grad_() for _ in range(3))
     do = torch.ones((b, h, n, d), device=dev, dtype=torch.bfloat16)  # gradient of o.sum()
     s = torch.tensor([2.0 ** (-8.0 * (i + 1) / h) for i in range(h)], device=dev).reshape(h, 1, 1)
-    fwd = event_time(torch, lambda: la.lightning_attn_func(q, k, v, s), 20, warm=5)
-    o = la.lightning_attn_func(q, k, v, s)
+    def fwd_bwd_ms(op):
+        fwd_ = event_time(torch, lambda: op(q, k, v, s), 20, warm=5)
+        o = op(q, k, v, s)
 
-    def bwd_fn():
-        q.grad = k.grad = v.grad = None
-        o.backward(do, retain_graph=True)
+        def bwd_fn():
+            q.grad = k.grad = v.grad = None
+            o.backward(do, retain_graph=True)
 
-    bwd = event_time(torch, bwd_fn, 20, warm=5)
+        return fwd_, event_time(torch, bwd_fn, 20, warm=5)
+
+    fwd, bwd = fwd_bwd_ms(la.lightning_attn_func)  # the public wrapper: d and e cut into slices of <= 128 for the fast kernels
+    fwd1, bwd1 = fwd_bwd_ms(la.lightning_attn2)    # one piece: the serial-phase kernel for dk > 128
     units = b * h * n
     gbs = 4224.0 * units / ((fwd + bwd) * 1e-3) / 1e9
     return {"shape": [b, h, n, d, d], "fwd_ms": fwd, "bwd_ms": bwd, "tokens_per_s": b * n / ((fwd + bwd) * 1e-3),
+            "one_piece_fwd_ms": fwd1, "one_piece_bwd_ms": bwd1,
             "alg_gbs": gbs, "hbm_frac": gbs / hbm_peak, "alg_tflops": 688128.0 * units / ((fwd + bwd) * 1e-3) / 1e12,
             "note": "20 back-to-back calls per event pair; the 4 x 18.9 MB working set fits L2, so this is a latency/occupancy "
                     "figure (24 (batch, head) pairs on 148 SMs: chunk mode), not a DRAM one"}

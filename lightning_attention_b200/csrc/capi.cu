@@ -502,6 +502,13 @@ int srms_dispatch(bool fwd, const void* x, const void* dy, void* out, float* rst
   LAB200_SRMS(32, 4)
   LAB200_SRMS(128, 2)
   LAB200_SRMS(128, 4)
+  // The backward kernel holds two tensors' vectors per thread: beyond four vectors each it runs out of resident CTAs to
+  // overlap one row's loads with another row's reduction and stores (5120-wide rows: 4.4 TB/s with 128 x 8), so wider
+  // groups come first there.
+  if (!fwd) {
+    LAB200_SRMS(256, 4)
+    LAB200_SRMS(512, 4)
+  }
   LAB200_SRMS(128, 8)
   LAB200_SRMS(256, 8)
   LAB200_SRMS(512, 8)

@@ -34,10 +34,6 @@
 #include <cuda_fp16.h>
 #include "ptx_sm100.cuh"
 
-#ifndef LA_P_IN_TMEM
-#define LA_P_IN_TMEM 0
-#endif
-
 namespace lab200 {
 
 constexpr int LA_BLOCK = 128;        // tokens per block
@@ -298,41 +294,6 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         issue_A(nxt);
         if (nstage == 2) issue_BC(nxt, stage ^ 1);
       }
-#if LA_P_IN_TMEM
-      {
-        // experiment: P goes back into TMEM (aliasing the first 64 columns of S) as the A operand of P C
-        uint32_t v[2][32];
-        bool deadt[2];
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c0 = hf * 64 + cc * 32;
-          deadt[cc] = reverse ? (c0 + 31 < q * 32) : (c0 > q * 32 + 31);
-          if (!deadt[cc]) tmem_ld32(tmem + lanebase + T_S + c0, v[cc]);
-        }
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        __syncthreads();  // every warp holds its part of S in registers before anyone overwrites it
-        tc_fence_after_sync();
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c0 = hf * 64 + cc * 32;
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float f0 = 0.f, f1 = 0.f;
-            if (!deadt[cc]) {
-              const int d0 = reverse ? (c0 + i - r) : (r - c0 - i);
-              const int d1 = reverse ? (d0 + 1) : (d0 - 1);
-              if (d0 >= 0) f0 = __uint_as_float(v[cc][i]) * decay_tab[d0];
-              if (d1 >= 0) f1 = __uint_as_float(v[cc][i + 1]) * decay_tab[d1];
-            }
-            pk[i >> 1] = pack2<FMT>(f0, f1);
-          }
-          tmem_st16(tmem + lanebase + T_S + (c0 >> 1), pk);
-        }
-        tmem_wait_st();
-      }
-#else
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c0 = hf * 64 + cc * 32;
@@ -361,7 +322,6 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           st_shared_v4(addr, pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
         }
       }
-#endif
     } else {
       if (tid == 0 && has_next && nstage == 2) issue_BC(nxt, stage ^ 1);
     }
@@ -395,12 +355,8 @@ la_chunk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (MODE == 0) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-#if LA_P_IN_TMEM
-          umma_f16_ts(tmem + T_OI, tmem + T_S + kk * 8, smem_desc_sw128(sCs + kk * 2048, SLAB), IDESC_PC, kk > 0);
-#else
           umma_f16(tmem + T_OI, smem_desc_sw128(sP + (kk >> 2) * SLAB + (kk & 3) * 32, 16),
                    smem_desc_sw128(sCs + kk * 2048, SLAB), IDESC_PC, kk > 0);
-#endif
         }
       }
 #pragma unroll
