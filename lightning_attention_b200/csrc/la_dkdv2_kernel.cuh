@@ -130,8 +130,15 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem = *tmem_slot;
 
 #define LD2_FAIL(code) { if (*fail_code == 0) *fail_code = (code); }
-#define LD2_TRACE(slot, it) if (p.trace != nullptr && bh == 0 && blockIdx.y == 0 && (it) < p.trace_blocks) \
+#define LD2_STAMP(slot, it) if (p.trace != nullptr && bh == 0 && blockIdx.y == 0 && (it) < p.trace_blocks) \
     p.trace[(it) * LA_TRACE_SLOTS + (slot)] = clock64();
+#ifdef LD2_MASK_TRACE  // debugging build: only the MMA warp's block start (slot 0) and the fine stamps of one mask warp
+#define LD2_TRACE(slot, it) if ((slot) == 0) { LD2_STAMP(slot, it) }
+#define LD2_TRACE_M(slot, it) LD2_STAMP(slot, it)
+#else
+#define LD2_TRACE(slot, it) LD2_STAMP(slot, it)
+#define LD2_TRACE_M(slot, it)
+#endif
 #define LD2_WAIT(which, it, code) if (!lap_wait(bar(which, it), par(it), abort_flag, budget)) { LD2_FAIL(code) break; }
 
   if (warp == 0) {
@@ -297,16 +304,19 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { LD2_FAIL(LA_ERR_WAIT_MMA1) alive = false; break; }
         if (q == 0 && lane == 0) { LD2_TRACE(8 + 2 * u, it) }
+        if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(15, it) }
         tc_fence_after_sync();
 #pragma unroll 1
         for (int t = 0; t < 4; ++t) {
           const int c0 = t * 32;
           const int kind = (t == q) ? 2 : ((t > q) ? 1 : 0);  // 0 dead, 1 live, 2 diagonal; warp-uniform
           uint32_t v[32];
+          if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(t * 3 + 1, it) }
           if (kind) {
             tmem_ld32(tmem + lanebase + T_S + c0, v);
             tmem_wait_ld();
           }
+          if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(t * 3 + 2, it) }
           uint32_t pk[16];
           if (kind == 1) {
             const float rowf = decay_tab[c0 - r];
@@ -314,31 +324,34 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int i = 0; i < 32; i += 2)
               pk[i >> 1] = pack2<FMT>(__uint_as_float(v[i]) * (rowf * g[i]), __uint_as_float(v[i + 1]) * (rowf * g[i + 1]));
           } else if (kind == 2 && diag_rank1) {
+            // Masked elements (column i < lane) are zeroed by AND-ing the value's bits with a sign mask, not by a select on
+            // the product: the compiler turned 32 selects into 32 branches per tile, and the diagonal tile, ~150 instructions
+            // otherwise, then took ~2,800 cycles (clock stamps), which made the mask passes the bound of the whole kernel.
             float rd = rowd;
             asm volatile("" : "+f"(rd));  // keeps the 32 products rd * g[i] from being hoisted out of the block loop into registers
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const int d0 = i - lane, d1 = d0 + 1;
-              const float f0 = (d0 >= 0) ? __uint_as_float(v[i]) * (rd * g[i]) : 0.f;
-              const float f1 = (d1 >= 0) ? __uint_as_float(v[i + 1]) * (rd * g[i + 1]) : 0.f;
-              pk[i >> 1] = pack2<FMT>(f0, f1);
+              const uint32_t k0 = ~static_cast<uint32_t>((i - lane) >> 31), k1 = ~static_cast<uint32_t>((i + 1 - lane) >> 31);
+              pk[i >> 1] = pack2<FMT>(__uint_as_float(v[i] & k0) * (rd * g[i]), __uint_as_float(v[i + 1] & k1) * (rd * g[i + 1]));
             }
           } else if (kind == 2) {
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               const int d0 = i - lane, d1 = d0 + 1;
+              const uint32_t k0 = ~static_cast<uint32_t>(d0 >> 31), k1 = ~static_cast<uint32_t>(d1 >> 31);
               const float m0 = decay_tab[max(d0, 0)], m1 = decay_tab[max(d1, 0)];
-              const float f0 = (d0 >= 0) ? __uint_as_float(v[i]) * m0 : 0.f;
-              const float f1 = (d1 >= 0) ? __uint_as_float(v[i + 1]) * m1 : 0.f;
-              pk[i >> 1] = pack2<FMT>(f0, f1);
+              pk[i >> 1] = pack2<FMT>(__uint_as_float(v[i] & k0) * m0, __uint_as_float(v[i + 1] & k1) * m1);
             }
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) pk[i] = 0u;
           }
           tmem_st16(tmem + lanebase + T_S + t * 16, pk);
+          if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(t * 3 + 3, it) }
         }
+        if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(13, it) }
         tmem_wait_st();
+        if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(14, it) }
         tc_fence_before_sync();
         mbar_arrive(bar(u ? LD2_P1_READY : LD2_P0_READY, it));
         if (q == 0 && lane == 0) { LD2_TRACE(9 + 2 * u, it) }
@@ -534,6 +547,8 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 #undef LD2_WAIT
 #undef LD2_TRACE
+#undef LD2_TRACE_M
+#undef LD2_STAMP
 #undef LD2_FAIL
 
   tc_fence_before_sync();
