@@ -437,12 +437,10 @@ def leg_config2(torch, la, dev, hbm_peak):
 
         return fwd_, event_time(torch, bwd_fn, 20, warm=5)
 
-    fwd, bwd = fwd_bwd_ms(la.lightning_attn_func)  # the public wrapper: d and e cut into slices of <= 128 for the fast kernels
-    fwd1, bwd1 = fwd_bwd_ms(la.lightning_attn2)    # one piece: the serial-phase kernel for dk > 128
+    fwd, bwd = fwd_bwd_ms(la.lightning_attn_func)  # the public wrapper (one piece: d, e <= 256)
     units = b * h * n
     gbs = 4224.0 * units / ((fwd + bwd) * 1e-3) / 1e9
     return {"shape": [b, h, n, d, d], "fwd_ms": fwd, "bwd_ms": bwd, "tokens_per_s": b * n / ((fwd + bwd) * 1e-3),
-            "one_piece_fwd_ms": fwd1, "one_piece_bwd_ms": bwd1,
             "alg_gbs": gbs, "hbm_frac": gbs / hbm_peak, "alg_tflops": 688128.0 * units / ((fwd + bwd) * 1e-3) / 1e12,
             "note": "20 back-to-back calls per event pair; the 4 x 18.9 MB working set fits L2, so this is a latency/occupancy "
                     "figure (24 (batch, head) pairs on 148 SMs: chunk mode), not a DRAM one"}
@@ -925,8 +923,6 @@ def main():
         srms2 = guarded(leg_srmsnorm, torch, la, L, dev, g, 2 * 32768, 5120, False)
         config2 = guarded(leg_config2, torch, la, dev, hbm_peak)
         sweep = guarded(leg_sweep, torch, la, dev, s)
-        if world == 1:
-            sustained = guarded(leg_sustained, torch, step, 2.0, local_rank)
 
     # ---- projection layout: q, k, v, do as (b, h, n, d) views of (b, n, h, d) tensors, as a caller's projections give them.
     # "in_place": the op reads and writes that layout directly. "with_copies": what the reference's wrapper does with such
@@ -1053,6 +1049,10 @@ def main():
         del hq, hk, hv, hdo, ho, hdq, hdk, hdv
     except Exception as ex:  # pinned allocation can fail on a small host
         e2e = {"value": None, "unit": "tokens/s", "error": repr(ex)[:200]}
+
+    # ---- sustained run of the headline step, last: it drives the GPU into its power cap, which would slow the legs after it
+    if rank == 0 and full and world == 1:
+        sustained = guarded(leg_sustained, torch, step, 2.0, local_rank)
 
     if rank == 0:
         units = B * H * N_TOK

@@ -479,10 +479,43 @@ void srms_launch(bool fwd, const void* x, const void* dy, void* out, float* rstd
   }
 }
 
+bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
+
+bool use_wide_srms_bwd() {
+  static const bool on = [] {
+    const char* e = getenv("LIGHTNING_B200_SRMS_WIDE");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <int DT, int G, int VPT>
+void srms_bwd_wide_launch(const void* x, const void* dy, void* out, const float* rstd, long long M, int N, cudaStream_t st) {
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  const unsigned grid = static_cast<unsigned>((M + RPC - 1) / RPC);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  srmsnorm_bwd_wide_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, dy, rstd, out, static_cast<int>(M), N);
+}
+
 template <int DT>
 int srms_dispatch(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
                   cudaStream_t st) {
   constexpr int EPV = SrmsVec<DT>::EPV;
+  // backward with 256-bit accesses when the rows allow it (a multiple of two 128-bit vectors, 32-byte aligned)
+  if (!fwd && use_wide_srms_bwd() && (N % (2 * EPV)) == 0 && aligned32(x) && aligned32(dy) && aligned32(out)) {
+    const int nw = N / (2 * EPV);
+#define LAB200_SRMSW(G, V) \
+    if (nw <= G * V) { srms_bwd_wide_launch<DT, G, V>(x, dy, out, rstd, M, N, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
+    LAB200_SRMSW(32, 1)
+    LAB200_SRMSW(32, 2)
+    LAB200_SRMSW(128, 1)
+    LAB200_SRMSW(128, 2)
+    LAB200_SRMSW(256, 2)
+    LAB200_SRMSW(512, 2)
+    LAB200_SRMSW(512, 4)
+#undef LAB200_SRMSW
+  }
   const bool vec_ok = (N % EPV == 0) && aligned16(x) && aligned16(out) && (fwd || aligned16(dy));
   if (!vec_ok) {
     const unsigned grid = static_cast<unsigned>(M);

@@ -70,15 +70,31 @@ template <> struct SrmsVec<SRMS_BF16> {
   }
 };
 
+#ifndef SRMS_LD_VARIANT
+#define SRMS_LD_VARIANT 0
+#endif
+#ifndef SRMS_ST_VARIANT
+#define SRMS_ST_VARIANT 0
+#endif
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
   uint4 v;
+#if SRMS_LD_VARIANT == 1
+  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v4.u32 {%0, %1, %2, %3}, [%4];"
+#else
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+#endif
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
 }
 __device__ __forceinline__ void st_stream(uint4* p, const uint4& v) {
+#if SRMS_ST_VARIANT == 1
+  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#elif SRMS_ST_VARIANT == 2
+  asm volatile("st.global.L1::no_allocate.L2::evict_first.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#else
   asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#endif
 }
 
 // Sum over the G threads that own one row. `slot` is this row group's scratch in shared memory.
@@ -188,6 +204,88 @@ srmsnorm_bwd_kernel(const void* __restrict__ x_, const void* __restrict__ dy_, c
 #pragma unroll
       for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
       st_stream(dx + v, V::pack(fg));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Backward pass with 256-bit global accesses (sm_100: ld/st .v8.b32), which also take an L2 eviction hint: x and dy are
+// read exactly once and dx is never read again, so all three are marked evict-first and do not push each other's
+// still-unread sectors out of L2. Same arithmetic as srmsnorm_bwd_kernel; rows must be a multiple of two 128-bit vectors
+// and 32-byte aligned. A "wide vector" is two uint4.
+// ---------------------------------------------------------------------------------------------------------------
+struct SrmsWide { uint4 lo, hi; };
+__device__ __forceinline__ SrmsWide ld_stream_wide(const void* p) {
+  SrmsWide v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream_wide(void* p, const SrmsWide& v) {
+  asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.u32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v.lo.x), "r"(v.lo.y),
+               "r"(v.lo.z), "r"(v.lo.w), "r"(v.hi.x), "r"(v.hi.y), "r"(v.hi.z), "r"(v.hi.w) : "memory");
+}
+
+template <int DT, int G, int VPT>
+__global__ void __launch_bounds__((G > 256 ? G : 256))
+srmsnorm_bwd_wide_kernel(const void* __restrict__ x_, const void* __restrict__ dy_, const float* __restrict__ rstd_,
+                         void* __restrict__ dx_, int M, int N) {
+  using V = SrmsVec<DT>;
+  constexpr int CTA = (G > 256 ? G : 256);
+  constexpr int RPC = CTA / G;
+  constexpr int EPW = 2 * V::EPV;  // elements per wide vector
+  __shared__ float red[RPC][16];
+  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
+  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
+  const bool active = row < M;
+  const int nw = N / EPW;
+  const size_t off = static_cast<size_t>(active ? row : 0) * nw;
+  const SrmsWide* x = reinterpret_cast<const SrmsWide*>(x_) + off;
+  const SrmsWide* dy = reinterpret_cast<const SrmsWide*>(dy_) + off;
+  SrmsWide* dx = reinterpret_cast<SrmsWide*>(dx_) + off;
+  const float rstd = active ? rstd_[row] : 0.f;
+
+  SrmsWide xv[VPT], gv[VPT];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nw) {
+      xv[i] = ld_stream_wide(x + v);
+      gv[i] = ld_stream_wide(dy + v);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nw) {
+      float fx[V::EPV], fg[V::EPV];
+      V::unpack(xv[i].lo, fx); V::unpack(gv[i].lo, fg);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fg[j], dot);
+      V::unpack(xv[i].hi, fx); V::unpack(gv[i].hi, fg);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fg[j], dot);
+    }
+  }
+  dot = group_sum<G>(dot, red[grp], tig);
+  const float c = dot / static_cast<float>(N);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tig + i * G;
+    if (active && v < nw) {
+      float fx[V::EPV], fg[V::EPV];
+      SrmsWide o;
+      V::unpack(xv[i].lo, fx); V::unpack(gv[i].lo, fg);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
+      o.lo = V::pack(fg);
+      V::unpack(xv[i].hi, fx); V::unpack(gv[i].hi, fg);
+#pragma unroll
+      for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
+      o.hi = V::pack(fg);
+      st_stream_wide(dx + v, o);
     }
   }
 }
