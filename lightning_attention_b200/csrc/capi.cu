@@ -465,23 +465,10 @@ int reset_status(void* workspace, size_t workspace_bytes, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------------
 // SRMSNorm launch selection
 // ---------------------------------------------------------------------------------------------
-template <int DT, int G, int VPT>
-void srms_launch(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
-                 cudaStream_t st) {
-  constexpr int CTA = (G > 256 ? G : 256);
-  constexpr int RPC = CTA / G;
-  const unsigned grid = static_cast<unsigned>((M + RPC - 1) / RPC);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  if (fwd) {
-    srmsnorm_fwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, out, rstd, static_cast<int>(M), N, eps);
-  } else {
-    srmsnorm_bwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, dy, rstd, out, static_cast<int>(M), N);
-  }
-}
-
 bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
-bool use_wide_srms_bwd() {
+// LIGHTNING_B200_SRMS_WIDE=0 keeps every SRMSNorm kernel on 128-bit accesses (A/B comparisons).
+bool use_wide_srms() {
   static const bool on = [] {
     const char* e = getenv("LIGHTNING_B200_SRMS_WIDE");
     return !(e && e[0] == '0');
@@ -489,33 +476,24 @@ bool use_wide_srms_bwd() {
   return on;
 }
 
-template <int DT, int G, int VPT>
-void srms_bwd_wide_launch(const void* x, const void* dy, void* out, const float* rstd, long long M, int N, cudaStream_t st) {
+template <int DT, int G, int VPT, int W>
+void srms_launch(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
+                 cudaStream_t st) {
   constexpr int CTA = (G > 256 ? G : 256);
   constexpr int RPC = CTA / G;
   const unsigned grid = static_cast<unsigned>((M + RPC - 1) / RPC);
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  srmsnorm_bwd_wide_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, dy, rstd, out, static_cast<int>(M), N);
+  if (fwd) {
+    srmsnorm_fwd_kernel<DT, G, VPT, W><<<grid, CTA, 0, st>>>(x, out, rstd, static_cast<int>(M), N, eps);
+  } else {
+    srmsnorm_bwd_kernel<DT, G, VPT, W><<<grid, CTA, 0, st>>>(x, dy, rstd, out, static_cast<int>(M), N);
+  }
 }
 
 template <int DT>
 int srms_dispatch(bool fwd, const void* x, const void* dy, void* out, float* rstd, long long M, int N, float eps,
                   cudaStream_t st) {
   constexpr int EPV = SrmsVec<DT>::EPV;
-  // backward with 256-bit accesses when the rows allow it (a multiple of two 128-bit vectors, 32-byte aligned)
-  if (!fwd && use_wide_srms_bwd() && (N % (2 * EPV)) == 0 && aligned32(x) && aligned32(dy) && aligned32(out)) {
-    const int nw = N / (2 * EPV);
-#define LAB200_SRMSW(G, V) \
-    if (nw <= G * V) { srms_bwd_wide_launch<DT, G, V>(x, dy, out, rstd, M, N, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
-    LAB200_SRMSW(32, 1)
-    LAB200_SRMSW(32, 2)
-    LAB200_SRMSW(128, 1)
-    LAB200_SRMSW(128, 2)
-    LAB200_SRMSW(256, 2)
-    LAB200_SRMSW(512, 2)
-    LAB200_SRMSW(512, 4)
-#undef LAB200_SRMSW
-  }
   const bool vec_ok = (N % EPV == 0) && aligned16(x) && aligned16(out) && (fwd || aligned16(dy));
   if (!vec_ok) {
     const unsigned grid = static_cast<unsigned>(M);
@@ -527,39 +505,51 @@ int srms_dispatch(bool fwd, const void* x, const void* dy, void* out, float* rst
     }
     return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
   }
-  const int nvec = N / EPV;
-  // smallest G * VPT that covers the row; two to four vectors per thread stream best (measured on 2048- and 4096-wide rows)
-#define LAB200_SRMS(G, V) \
-  if (nvec <= G * V) { srms_launch<DT, G, V>(fwd, x, dy, out, rstd, M, N, eps, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
-  LAB200_SRMS(32, 2)
-  LAB200_SRMS(32, 4)
-  LAB200_SRMS(128, 2)
-  LAB200_SRMS(128, 4)
-  // The backward kernel holds two tensors' vectors per thread: beyond four vectors each it runs out of resident CTAs to
-  // overlap one row's loads with another row's reduction and stores (5120-wide rows: 4.4 TB/s with 128 x 8), so wider
-  // groups come first there.
-  if (!fwd) {
-    LAB200_SRMS(256, 4)
-    LAB200_SRMS(512, 4)
+#define LAB200_SRMS(G, V, W) \
+  if (np <= G * V) { srms_launch<DT, G, V, W>(fwd, x, dy, out, rstd, M, N, eps, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
+  // 256-bit accesses with L2 evict-first hints when the rows allow it (a multiple of two vectors, 32-byte aligned): one or two
+  // packs per thread (the backward kernel holds two tensors' packs; with more per thread too few CTAs are resident to
+  // overlap one row's loads with another row's reduction and stores)
+  if (use_wide_srms() && (N % (2 * EPV)) == 0 && aligned32(x) && aligned32(out) && (fwd || aligned32(dy))) {
+    const int np = N / (2 * EPV);
+    LAB200_SRMS(32, 1, 2)
+    LAB200_SRMS(32, 2, 2)
+    LAB200_SRMS(128, 1, 2)
+    LAB200_SRMS(128, 2, 2)
+    LAB200_SRMS(256, 2, 2)
+    LAB200_SRMS(512, 2, 2)
+    LAB200_SRMS(512, 4, 2)
   }
-  LAB200_SRMS(128, 8)
-  LAB200_SRMS(256, 8)
-  LAB200_SRMS(512, 8)
+  {
+    const int np = N / EPV;
+    // smallest G * VPT that covers the row; two to four vectors per thread stream best (measured on 2048- and 4096-wide rows)
+    LAB200_SRMS(32, 2, 1)
+    LAB200_SRMS(32, 4, 1)
+    LAB200_SRMS(128, 2, 1)
+    LAB200_SRMS(128, 4, 1)
+    if (!fwd) {
+      LAB200_SRMS(256, 4, 1)
+      LAB200_SRMS(512, 4, 1)
+    }
+    LAB200_SRMS(128, 8, 1)
+    LAB200_SRMS(256, 8, 1)
+    LAB200_SRMS(512, 8, 1)
+  }
 #undef LAB200_SRMS
   return LAB200_ERR_SHAPE;
 }
 
 // Gated SRMSNorm: vectorised rows only (row length a multiple of the vector width, 16-byte aligned pointers, at most
 // 2048 vectors so that three rows' worth of registers fit); callers compose the plain kernels otherwise.
-template <int DT, int G, int VPT>
+template <int DT, int G, int VPT, int W>
 void srms_gate_launch(bool fwd, const void* x, const void* g, const void* dy, void* out, void* dg, float* rstd, long long M,
                       int N, float eps, cudaStream_t st) {
   constexpr int CTA = (G > 256 ? G : 256);
   constexpr int RPC = CTA / G;
   const unsigned grid = static_cast<unsigned>((M + RPC - 1) / RPC);
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  if (fwd) srmsnorm_gate_fwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, g, out, rstd, static_cast<int>(M), N, eps);
-  else srmsnorm_gate_bwd_kernel<DT, G, VPT><<<grid, CTA, 0, st>>>(x, g, dy, rstd, out, dg, static_cast<int>(M), N);
+  if (fwd) srmsnorm_gate_fwd_kernel<DT, G, VPT, W><<<grid, CTA, 0, st>>>(x, g, out, rstd, static_cast<int>(M), N, eps);
+  else srmsnorm_gate_bwd_kernel<DT, G, VPT, W><<<grid, CTA, 0, st>>>(x, g, dy, rstd, out, dg, static_cast<int>(M), N);
 }
 
 template <int DT>
@@ -568,15 +558,28 @@ int srms_gate_dispatch(bool fwd, const void* x, const void* g, const void* dy, v
   constexpr int EPV = SrmsVec<DT>::EPV;
   if ((N % EPV) != 0) return LAB200_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(g) || !aligned16(out) || (!fwd && (!aligned16(dy) || !aligned16(dg)))) return LAB200_ERR_ALIGN;
-  const int nvec = N / EPV;
-#define LAB200_SRMSG(G, V) \
-  if (nvec <= G * V) { srms_gate_launch<DT, G, V>(fwd, x, g, dy, out, dg, rstd, M, N, eps, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
-  LAB200_SRMSG(32, 2)
-  LAB200_SRMSG(32, 4)
-  LAB200_SRMSG(128, 2)
-  LAB200_SRMSG(128, 4)
-  LAB200_SRMSG(256, 4)
-  LAB200_SRMSG(512, 4)
+  if (N / EPV > 2048) return LAB200_ERR_SHAPE;
+#define LAB200_SRMSG(G, V, W) \
+  if (np <= G * V) { srms_gate_launch<DT, G, V, W>(fwd, x, g, dy, out, dg, rstd, M, N, eps, st); return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA; }
+  if (use_wide_srms() && (N % (2 * EPV)) == 0 && aligned32(x) && aligned32(g) && aligned32(out) &&
+      (fwd || (aligned32(dy) && aligned32(dg)))) {
+    const int np = N / (2 * EPV);
+    LAB200_SRMSG(32, 1, 2)
+    LAB200_SRMSG(32, 2, 2)
+    LAB200_SRMSG(128, 1, 2)
+    LAB200_SRMSG(128, 2, 2)
+    LAB200_SRMSG(256, 2, 2)
+    LAB200_SRMSG(512, 2, 2)
+  }
+  {
+    const int np = N / EPV;
+    LAB200_SRMSG(32, 2, 1)
+    LAB200_SRMSG(32, 4, 1)
+    LAB200_SRMSG(128, 2, 1)
+    LAB200_SRMSG(128, 4, 1)
+    LAB200_SRMSG(256, 4, 1)
+    LAB200_SRMSG(512, 4, 1)
+  }
 #undef LAB200_SRMSG
   return LAB200_ERR_SHAPE;
 }

@@ -70,31 +70,34 @@ template <> struct SrmsVec<SRMS_BF16> {
   }
 };
 
-#ifndef SRMS_LD_VARIANT
-#define SRMS_LD_VARIANT 0
-#endif
-#ifndef SRMS_ST_VARIANT
-#define SRMS_ST_VARIANT 0
-#endif
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
-  uint4 v;
-#if SRMS_LD_VARIANT == 1
-  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v4.u32 {%0, %1, %2, %3}, [%4];"
-#else
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-#endif
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
+// A thread's unit of global access: W = 1 is one 128-bit vector, W = 2 one 256-bit access (sm_100: ld/st .v8.b32). The
+// 256-bit forms also take an L2 eviction hint: every input is read exactly once and no output is read again, so all of them
+// are marked evict-first and do not push each other's still-unread sectors out of L2 (measured on 32768 x 4096 bf16 rows:
+// backward 5.8 -> 6.8 TB/s). W = 2 needs rows that are a multiple of two vectors and 32-byte aligned pointers.
+template <int W> struct SrmsPack { uint4 q[W]; };
+
+template <int W>
+__device__ __forceinline__ SrmsPack<W> ld_stream(const SrmsPack<W>* p) {
+  SrmsPack<W> v;
+  if constexpr (W == 2) {
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v.q[0].x), "=r"(v.q[0].y), "=r"(v.q[0].z), "=r"(v.q[0].w), "=r"(v.q[1].x), "=r"(v.q[1].y), "=r"(v.q[1].z), "=r"(v.q[1].w)
+                 : "l"(p));
+  } else {
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.q[0].x), "=r"(v.q[0].y), "=r"(v.q[0].z), "=r"(v.q[0].w)
+                 : "l"(p));
+  }
   return v;
 }
-__device__ __forceinline__ void st_stream(uint4* p, const uint4& v) {
-#if SRMS_ST_VARIANT == 1
-  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-#elif SRMS_ST_VARIANT == 2
-  asm volatile("st.global.L1::no_allocate.L2::evict_first.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-#else
-  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-#endif
+template <int W>
+__device__ __forceinline__ void st_stream(SrmsPack<W>* p, const SrmsPack<W>& v) {
+  if constexpr (W == 2) {
+    asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.u32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v.q[0].x),
+                 "r"(v.q[0].y), "r"(v.q[0].z), "r"(v.q[0].w), "r"(v.q[1].x), "r"(v.q[1].y), "r"(v.q[1].z), "r"(v.q[1].w) : "memory");
+  } else {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.q[0].x), "r"(v.q[0].y), "r"(v.q[0].z), "r"(v.q[0].w) : "memory");
+  }
 }
 
 // Sum over the G threads that own one row. `slot` is this row group's scratch in shared memory.
@@ -115,177 +118,130 @@ __device__ __forceinline__ float group_sum(float v, float* slot, int tig) {
   return v;
 }
 
-// G threads per row holding VPT vectors each; CTA = max(G, 256) threads => CTA / G rows per CTA.
-template <int DT, int G, int VPT>
+// Row bookkeeping shared by the four kernels: G threads per row holding VPT packs each; CTA = max(G, 256) threads =>
+// CTA / G rows per CTA. Whole groups are (in)active together; inactive ones still reach the barriers.
+template <int DT, int G, int W>
+struct SrmsRow {
+  using V = SrmsVec<DT>;
+  static constexpr int CTA = (G > 256 ? G : 256);
+  static constexpr int RPC = CTA / G;
+  static constexpr int EPP = W * V::EPV;  // elements per pack
+  int grp, tig, npack;
+  long long row;
+  bool active;
+  size_t off;
+  __device__ SrmsRow(int M, int N) {
+    grp = threadIdx.x / G; tig = threadIdx.x % G;
+    row = static_cast<long long>(blockIdx.x) * RPC + grp;
+    active = row < M;
+    npack = N / EPP;
+    off = static_cast<size_t>(active ? row : 0) * npack;
+  }
+};
+
+template <int DT, int G, int VPT, int W>
 __global__ void __launch_bounds__((G > 256 ? G : 256))
 srmsnorm_fwd_kernel(const void* __restrict__ x_, void* __restrict__ y_, float* __restrict__ rstd_, int M, int N, float eps) {
-  using V = SrmsVec<DT>;
-  constexpr int CTA = (G > 256 ? G : 256);
-  constexpr int RPC = CTA / G;
-  __shared__ float red[RPC][16];
-  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
-  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
-  const bool active = row < M;  // whole groups are (in)active together; inactive ones still reach the barriers
-  const int nvec = N / V::EPV;
-  const uint4* x = reinterpret_cast<const uint4*>(x_) + (active ? row : 0) * nvec;
-  uint4* y = reinterpret_cast<uint4*>(y_) + (active ? row : 0) * nvec;
+  using R = SrmsRow<DT, G, W>; using V = SrmsVec<DT>; using P = SrmsPack<W>;
+  __shared__ float red[R::RPC][16];
+  const R r(M, N);
+  const P* x = reinterpret_cast<const P*>(x_) + r.off;
+  P* y = reinterpret_cast<P*>(y_) + r.off;
 
-  uint4 xv[VPT];
+  P xv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) xv[i] = ld_stream<W>(x + v);
+  }
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      xv[i] = ld_stream(x + v);
-      float f[V::EPV];
-      V::unpack(xv[i], f);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) ss = fmaf(f[j], f[j], ss);
+      for (int w = 0; w < W; ++w) {
+        float f[V::EPV];
+        V::unpack(xv[i].q[w], f);
+#pragma unroll
+        for (int j = 0; j < V::EPV; ++j) ss = fmaf(f[j], f[j], ss);
+      }
     }
   }
-  ss = group_sum<G>(ss, red[grp], tig);
+  ss = group_sum<G>(ss, red[r.grp], r.tig);
   const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
-  if (active && tig == 0) rstd_[row] = rstd;
+  if (r.active && r.tig == 0) rstd_[r.row] = rstd;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      float f[V::EPV];
-      V::unpack(xv[i], f);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
+      P o;
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) f[j] *= rstd;
-      st_stream(y + v, V::pack(f));
+      for (int w = 0; w < W; ++w) {
+        float f[V::EPV];
+        V::unpack(xv[i].q[w], f);
+#pragma unroll
+        for (int j = 0; j < V::EPV; ++j) f[j] *= rstd;
+        o.q[w] = V::pack(f);
+      }
+      st_stream<W>(y + v, o);
     }
   }
 }
 
-template <int DT, int G, int VPT>
+template <int DT, int G, int VPT, int W>
 __global__ void __launch_bounds__((G > 256 ? G : 256))
 srmsnorm_bwd_kernel(const void* __restrict__ x_, const void* __restrict__ dy_, const float* __restrict__ rstd_,
                     void* __restrict__ dx_, int M, int N) {
-  using V = SrmsVec<DT>;
-  constexpr int CTA = (G > 256 ? G : 256);
-  constexpr int RPC = CTA / G;
-  __shared__ float red[RPC][16];
-  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
-  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
-  const bool active = row < M;
-  const int nvec = N / V::EPV;
-  const size_t off = static_cast<size_t>(active ? row : 0) * nvec;
-  const uint4* x = reinterpret_cast<const uint4*>(x_) + off;
-  const uint4* dy = reinterpret_cast<const uint4*>(dy_) + off;
-  uint4* dx = reinterpret_cast<uint4*>(dx_) + off;
-  const float rstd = active ? rstd_[row] : 0.f;
+  using R = SrmsRow<DT, G, W>; using V = SrmsVec<DT>; using P = SrmsPack<W>;
+  __shared__ float red[R::RPC][16];
+  const R r(M, N);
+  const P* x = reinterpret_cast<const P*>(x_) + r.off;
+  const P* dy = reinterpret_cast<const P*>(dy_) + r.off;
+  P* dx = reinterpret_cast<P*>(dx_) + r.off;
+  const float rstd = r.active ? rstd_[r.row] : 0.f;
 
-  uint4 xv[VPT], gv[VPT];
+  P xv[VPT], gv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
+      xv[i] = ld_stream<W>(x + v);
+      gv[i] = ld_stream<W>(dy + v);
+    }
+  }
   float dot = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      xv[i] = ld_stream(x + v);
-      gv[i] = ld_stream(dy + v);
-      float fx[V::EPV], fg[V::EPV];
-      V::unpack(xv[i], fx);
-      V::unpack(gv[i], fg);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fg[j], dot);
+      for (int w = 0; w < W; ++w) {
+        float fx[V::EPV], fg[V::EPV];
+        V::unpack(xv[i].q[w], fx);
+        V::unpack(gv[i].q[w], fg);
+#pragma unroll
+        for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fg[j], dot);
+      }
     }
   }
-  dot = group_sum<G>(dot, red[grp], tig);
+  dot = group_sum<G>(dot, red[r.grp], r.tig);
   const float c = dot / static_cast<float>(N);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      float fx[V::EPV], fg[V::EPV];
-      V::unpack(xv[i], fx);
-      V::unpack(gv[i], fg);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
+      P o;
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
-      st_stream(dx + v, V::pack(fg));
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------------------
-// Backward pass with 256-bit global accesses (sm_100: ld/st .v8.b32), which also take an L2 eviction hint: x and dy are
-// read exactly once and dx is never read again, so all three are marked evict-first and do not push each other's
-// still-unread sectors out of L2. Same arithmetic as srmsnorm_bwd_kernel; rows must be a multiple of two 128-bit vectors
-// and 32-byte aligned. A "wide vector" is two uint4.
-// ---------------------------------------------------------------------------------------------------------------
-struct SrmsWide { uint4 lo, hi; };
-__device__ __forceinline__ SrmsWide ld_stream_wide(const void* p) {
-  SrmsWide v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
-               : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void st_stream_wide(void* p, const SrmsWide& v) {
-  asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.u32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v.lo.x), "r"(v.lo.y),
-               "r"(v.lo.z), "r"(v.lo.w), "r"(v.hi.x), "r"(v.hi.y), "r"(v.hi.z), "r"(v.hi.w) : "memory");
-}
-
-template <int DT, int G, int VPT>
-__global__ void __launch_bounds__((G > 256 ? G : 256))
-srmsnorm_bwd_wide_kernel(const void* __restrict__ x_, const void* __restrict__ dy_, const float* __restrict__ rstd_,
-                         void* __restrict__ dx_, int M, int N) {
-  using V = SrmsVec<DT>;
-  constexpr int CTA = (G > 256 ? G : 256);
-  constexpr int RPC = CTA / G;
-  constexpr int EPW = 2 * V::EPV;  // elements per wide vector
-  __shared__ float red[RPC][16];
-  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
-  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
-  const bool active = row < M;
-  const int nw = N / EPW;
-  const size_t off = static_cast<size_t>(active ? row : 0) * nw;
-  const SrmsWide* x = reinterpret_cast<const SrmsWide*>(x_) + off;
-  const SrmsWide* dy = reinterpret_cast<const SrmsWide*>(dy_) + off;
-  SrmsWide* dx = reinterpret_cast<SrmsWide*>(dx_) + off;
-  const float rstd = active ? rstd_[row] : 0.f;
-
-  SrmsWide xv[VPT], gv[VPT];
-  float dot = 0.f;
+      for (int w = 0; w < W; ++w) {
+        float fx[V::EPV], fg[V::EPV];
+        V::unpack(xv[i].q[w], fx);
+        V::unpack(gv[i].q[w], fg);
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nw) {
-      xv[i] = ld_stream_wide(x + v);
-      gv[i] = ld_stream_wide(dy + v);
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nw) {
-      float fx[V::EPV], fg[V::EPV];
-      V::unpack(xv[i].lo, fx); V::unpack(gv[i].lo, fg);
-#pragma unroll
-      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fg[j], dot);
-      V::unpack(xv[i].hi, fx); V::unpack(gv[i].hi, fg);
-#pragma unroll
-      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fg[j], dot);
-    }
-  }
-  dot = group_sum<G>(dot, red[grp], tig);
-  const float c = dot / static_cast<float>(N);
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nw) {
-      float fx[V::EPV], fg[V::EPV];
-      SrmsWide o;
-      V::unpack(xv[i].lo, fx); V::unpack(gv[i].lo, fg);
-#pragma unroll
-      for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
-      o.lo = V::pack(fg);
-      V::unpack(xv[i].hi, fx); V::unpack(gv[i].hi, fg);
-#pragma unroll
-      for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
-      o.hi = V::pack(fg);
-      st_stream_wide(dx + v, o);
+        for (int j = 0; j < V::EPV; ++j) fg[j] = (fg[j] - fx[j] * rstd * c) * rstd;
+        o.q[w] = V::pack(fg);
+      }
+      st_stream<W>(dx + v, o);
     }
   }
 }
@@ -297,111 +253,128 @@ srmsnorm_bwd_wide_kernel(const void* __restrict__ x_, const void* __restrict__ d
 // One pass each instead of norm + sigmoid + multiply as three kernels (14 and 26 bytes per element).
 __device__ __forceinline__ float sigmoidf_fast(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
 
-template <int DT, int G, int VPT>
+template <int DT, int G, int VPT, int W>
 __global__ void __launch_bounds__((G > 256 ? G : 256))
 srmsnorm_gate_fwd_kernel(const void* __restrict__ x_, const void* __restrict__ g_, void* __restrict__ y_,
                          float* __restrict__ rstd_, int M, int N, float eps) {
-  using V = SrmsVec<DT>;
-  constexpr int CTA = (G > 256 ? G : 256);
-  constexpr int RPC = CTA / G;
-  __shared__ float red[RPC][16];
-  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
-  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
-  const bool active = row < M;
-  const int nvec = N / V::EPV;
-  const size_t off = static_cast<size_t>(active ? row : 0) * nvec;
-  const uint4* x = reinterpret_cast<const uint4*>(x_) + off;
-  const uint4* g = reinterpret_cast<const uint4*>(g_) + off;
-  uint4* y = reinterpret_cast<uint4*>(y_) + off;
+  using R = SrmsRow<DT, G, W>; using V = SrmsVec<DT>; using P = SrmsPack<W>;
+  __shared__ float red[R::RPC][16];
+  const R r(M, N);
+  const P* x = reinterpret_cast<const P*>(x_) + r.off;
+  const P* g = reinterpret_cast<const P*>(g_) + r.off;
+  P* y = reinterpret_cast<P*>(y_) + r.off;
 
-  uint4 xv[VPT], gv[VPT];
+  P xv[VPT], gv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
+      xv[i] = ld_stream<W>(x + v);
+      gv[i] = ld_stream<W>(g + v);
+    }
+  }
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      xv[i] = ld_stream(x + v);
-      gv[i] = ld_stream(g + v);
-      float f[V::EPV];
-      V::unpack(xv[i], f);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) ss = fmaf(f[j], f[j], ss);
+      for (int w = 0; w < W; ++w) {
+        float f[V::EPV];
+        V::unpack(xv[i].q[w], f);
+#pragma unroll
+        for (int j = 0; j < V::EPV; ++j) ss = fmaf(f[j], f[j], ss);
+      }
     }
   }
-  ss = group_sum<G>(ss, red[grp], tig);
+  ss = group_sum<G>(ss, red[r.grp], r.tig);
   const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
-  if (active && tig == 0) rstd_[row] = rstd;
+  if (r.active && r.tig == 0) rstd_[r.row] = rstd;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      float f[V::EPV], fg[V::EPV];
-      V::unpack(xv[i], f);
-      V::unpack(gv[i], fg);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
+      P o;
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) f[j] = f[j] * rstd * sigmoidf_fast(fg[j]);
-      st_stream(y + v, V::pack(f));
+      for (int w = 0; w < W; ++w) {
+        float f[V::EPV], fg[V::EPV];
+        V::unpack(xv[i].q[w], f);
+        V::unpack(gv[i].q[w], fg);
+#pragma unroll
+        for (int j = 0; j < V::EPV; ++j) f[j] = f[j] * rstd * sigmoidf_fast(fg[j]);
+        o.q[w] = V::pack(f);
+      }
+      st_stream<W>(y + v, o);
     }
   }
 }
 
-template <int DT, int G, int VPT>
+template <int DT, int G, int VPT, int W>
 __global__ void __launch_bounds__((G > 256 ? G : 256))
 srmsnorm_gate_bwd_kernel(const void* __restrict__ x_, const void* __restrict__ g_, const void* __restrict__ dy_,
                          const float* __restrict__ rstd_, void* __restrict__ dx_, void* __restrict__ dg_, int M, int N) {
-  using V = SrmsVec<DT>;
-  constexpr int CTA = (G > 256 ? G : 256);
-  constexpr int RPC = CTA / G;
-  __shared__ float red[RPC][16];
-  const int grp = threadIdx.x / G, tig = threadIdx.x % G;
-  const long long row = static_cast<long long>(blockIdx.x) * RPC + grp;
-  const bool active = row < M;
-  const int nvec = N / V::EPV;
-  const size_t off = static_cast<size_t>(active ? row : 0) * nvec;
-  const uint4* x = reinterpret_cast<const uint4*>(x_) + off;
-  const uint4* g = reinterpret_cast<const uint4*>(g_) + off;
-  const uint4* dy = reinterpret_cast<const uint4*>(dy_) + off;
-  uint4* dx = reinterpret_cast<uint4*>(dx_) + off;
-  uint4* dg = reinterpret_cast<uint4*>(dg_) + off;
-  const float rstd = active ? rstd_[row] : 0.f;
+  using R = SrmsRow<DT, G, W>; using V = SrmsVec<DT>; using P = SrmsPack<W>;
+  __shared__ float red[R::RPC][16];
+  const R r(M, N);
+  const P* x = reinterpret_cast<const P*>(x_) + r.off;
+  const P* g = reinterpret_cast<const P*>(g_) + r.off;
+  const P* dy = reinterpret_cast<const P*>(dy_) + r.off;
+  P* dx = reinterpret_cast<P*>(dx_) + r.off;
+  P* dg = reinterpret_cast<P*>(dg_) + r.off;
+  const float rstd = r.active ? rstd_[r.row] : 0.f;
 
-  uint4 xv[VPT], gv[VPT], dv[VPT];
+  P xv[VPT], gv[VPT], dv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
+      xv[i] = ld_stream<W>(x + v);
+      gv[i] = ld_stream<W>(g + v);
+      dv[i] = ld_stream<W>(dy + v);
+    }
+  }
   float dot = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      xv[i] = ld_stream(x + v);
-      gv[i] = ld_stream(g + v);
-      dv[i] = ld_stream(dy + v);
-      float fx[V::EPV], fg[V::EPV], fd[V::EPV];
-      V::unpack(xv[i], fx);
-      V::unpack(gv[i], fg);
-      V::unpack(dv[i], fd);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fd[j] * sigmoidf_fast(fg[j]), dot);
+      for (int w = 0; w < W; ++w) {
+        float fx[V::EPV], fg[V::EPV], fd[V::EPV];
+        V::unpack(xv[i].q[w], fx);
+        V::unpack(gv[i].q[w], fg);
+        V::unpack(dv[i].q[w], fd);
+#pragma unroll
+        for (int j = 0; j < V::EPV; ++j) dot = fmaf(fx[j] * rstd, fd[j] * sigmoidf_fast(fg[j]), dot);
+      }
     }
   }
-  dot = group_sum<G>(dot, red[grp], tig);
+  dot = group_sum<G>(dot, red[r.grp], r.tig);
   const float c = dot / static_cast<float>(N);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = tig + i * G;
-    if (active && v < nvec) {
-      float fx[V::EPV], fg[V::EPV], fd[V::EPV];
-      V::unpack(xv[i], fx);
-      V::unpack(gv[i], fg);
-      V::unpack(dv[i], fd);
+    const int v = r.tig + i * G;
+    if (r.active && v < r.npack) {
+      P ox, og;
 #pragma unroll
-      for (int j = 0; j < V::EPV; ++j) {
-        const float sg = sigmoidf_fast(fg[j]);
-        const float xh = fx[j] * rstd;
-        const float t = fd[j] * sg;
-        fg[j] = fd[j] * xh * sg * (1.0f - sg);  // dg
-        fx[j] = (t - xh * c) * rstd;            // dx
+      for (int w = 0; w < W; ++w) {
+        float fx[V::EPV], fg[V::EPV], fd[V::EPV];
+        V::unpack(xv[i].q[w], fx);
+        V::unpack(gv[i].q[w], fg);
+        V::unpack(dv[i].q[w], fd);
+#pragma unroll
+        for (int j = 0; j < V::EPV; ++j) {
+          const float sg = sigmoidf_fast(fg[j]);
+          const float xh = fx[j] * rstd;
+          const float t = fd[j] * sg;
+          fg[j] = fd[j] * xh * sg * (1.0f - sg);  // dg
+          fx[j] = (t - xh * c) * rstd;            // dx
+        }
+        ox.q[w] = V::pack(fx);
+        og.q[w] = V::pack(fg);
       }
-      st_stream(dx + v, V::pack(fx));
-      st_stream(dg + v, V::pack(fg));
+      st_stream<W>(dx + v, ox);
+      st_stream<W>(dg + v, og);
     }
   }
 }
