@@ -162,6 +162,16 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int blk = blk_of(it);
         const int st = it & 1;
         alive = false;
+#if defined(LD2_PF)
+        if (it + 1 < nb) {
+          const int nblk = blk_of(it + 1);
+          for (int sl = 0; sl < NE; ++sl) tma_prefetch_l2_3d(&tmV, sl * 64, nblk * LA_BLOCK, zc);
+          for (int sl = 0; sl < ND; ++sl) tma_prefetch_l2_3d(&tmK, sl * 64, nblk * LA_BLOCK, zc);
+#if LD2_PF >= 2
+          for (int sl = 0; sl < 2; ++sl) tma_prefetch_l2_3d(&tmQ, sl * 64, nblk * LA_BLOCK, zc);
+#endif
+        }
+#endif
         // do: P1 do of block it-2 was the last reader of this stage
         if (it >= 2) { LD2_WAIT(LD2_PC1_DONE, it - 2, LA_ERR_WAIT_MMA2) }
         mbar_arrive_expect_tx(bar(LD2_FULL_G, it), NE * SLAB);
