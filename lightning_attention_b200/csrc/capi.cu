@@ -348,7 +348,7 @@ int launch_dkdv_one(const CUtensorMap (&tm)[6], const LaDkdvParams& p, dim3 grid
     cudaGetLastError();
     return LAB200_ERR_CUDA;
   }
-  kern<<<grid, LAP_THREADS, smem, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], p);
+  kern<<<grid, LD2_THREADS, smem, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? LAB200_OK : LAB200_ERR_CUDA;
 }

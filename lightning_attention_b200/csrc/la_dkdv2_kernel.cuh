@@ -16,13 +16,21 @@
 //                                                                                    term is a second K range of the same
 //                                                                                    tcgen05.mma chain, A read from TMEM)
 //   D  = (lambda^r q)^T do ;  dKV <- lambda^128 dKV + D                             (fp32 registers + bf16 copy in smem)
-// Shared memory: do double-buffered; q, k, v single-buffered (k and v are free as soon as their S product and scaled copy
-// are done; q is free once D, issued right after the dk half, has read it); one 32 KB staging buffer through which the dk
-// tile and then the dv tile of a block leave by TMA store (row-per-thread stores straight from registers to global
-// memory were measured 1500 cycles per block slower: 32 distinct lines per warp instruction).
+// Shared memory: do double-buffered; q, k, v single-buffered; one 32 KB staging buffer through which the dk tile and then
+// the dv tile of a block leave by TMA store (row-per-thread stores straight from registers to global memory were measured
+// 1500 cycles per block slower: 32 distinct lines per warp instruction).
 //
-// Roles: warp 0 TMA producer, warp 1 MMA issuer (one thread), warps 2-5 mask group (one per TMEM lane quadrant),
-// warps 6-13 state/output group. Every wait is bounded and polls a CTA-wide abort flag.
+// Every single-buffered tile is released as early as its readers allow, and the chain from one load of it to the next holds
+// nothing else (a tile load takes 2,200-3,000 cycles under full load):
+//   q: load -> S1, P0 q (commit QP_DONE) -> rows scaled in place (state group) -> D (commit D_DONE) -> next load
+//   k: load -> S1 -> mask pass 1 -> scaled copy Ks, by the same warps (PK1_READY) -> next load
+//   v: load -> S0 (issued one block ahead) -> mask pass 0 -> scaled copy Vs (PV0_READY) -> next load
+// Roles (480 threads): warp 0 issues the loads, in the order in which their buffers come free; warp 1 issues the MMAs (one
+// elected thread), per block: P0 q | Vs dKV^T | S0 of the next block | D | P1 do + Ks dKV | S1 of the next block; warps 2-5
+// are the mask group (one per TMEM lane quadrant), which also writes the scaled copies right behind its own mask passes;
+// warps 6-13 are the state/output group (q scaling, the two output tiles, the state recurrence and its bf16 copy); warp 14
+// stores the staged output tiles, so that waiting for a store to have read the staging buffer never delays a load.
+// Every wait is bounded and polls a CTA-wide abort flag.
 #pragma once
 #include <type_traits>
 
@@ -43,16 +51,21 @@ struct LaDkdvParams {
   int trace_blocks;
 };
 
+constexpr int LD2_THREADS = 480;  // 15 warps: 65536 / 480 still allows 128 registers per thread
+
 // barrier slots; every slot has two instances indexed by block parity
 enum : int {
   LD2_FULL_Q = 0, LD2_FULL_G, LD2_FULL_V, LD2_FULL_K,
-  LD2_S0_READY, LD2_S1_READY, LD2_P0_READY, LD2_P1_READY, LD2_VS_READY, LD2_KS_READY,
+  LD2_S0_READY, LD2_S1_READY,
+  LD2_PV0_READY,  // P0 and the scaled copy Vs are in SA (mask group); v may be reloaded
+  LD2_PK1_READY,  // P1 and the scaled copy Ks are in SB (mask group); k may be reloaded
+  LD2_QP_DONE,    // S1 and P0 q have read the unscaled q tile
   LD2_PC0_DONE, LD2_PC1_DONE, LD2_O_FREE0, LD2_O_FREE1, LD2_O_STAGED0, LD2_O_STAGED1, LD2_BUF_FREE0, LD2_BUF_FREE1,
   LD2_Q_SCALED, LD2_D_DONE, LD2_D_FREE, LD2_STATE_READY, LD2_NUM_BARS
 };
 
 template <int ND, int NE, int FMT>
-__global__ void __launch_bounds__(LAP_THREADS, 1)
+__global__ void __launch_bounds__(LD2_THREADS, 1)
 la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
                 const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV, const LaDkdvParams p) {
@@ -106,9 +119,9 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (tid == 0) {
     for (int i = 0; i < LD2_NUM_BARS; ++i) {
       uint32_t count = 1u;
-      if (i == LD2_P0_READY || i == LD2_P1_READY) count = LAP_MASK_THREADS;
-      if (i == LD2_VS_READY || i == LD2_KS_READY || i == LD2_O_FREE0 || i == LD2_O_FREE1 || i == LD2_Q_SCALED ||
-          i == LD2_D_FREE || i == LD2_STATE_READY || i == LD2_O_STAGED0 || i == LD2_O_STAGED1)
+      if (i == LD2_PV0_READY || i == LD2_PK1_READY) count = LAP_MASK_THREADS;
+      if (i == LD2_O_FREE0 || i == LD2_O_FREE1 || i == LD2_Q_SCALED || i == LD2_D_FREE || i == LD2_STATE_READY ||
+          i == LD2_O_STAGED0 || i == LD2_O_STAGED1)
         count = LAP_STATE_THREADS;
       mbar_init(sBar + (i * 2) * 8, count);
       mbar_init(sBar + (i * 2 + 1) * 8, count);
@@ -129,81 +142,116 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
+#ifdef LD2_WAITACC  // debugging build: every thread sums the cycles it spends inside bounded waits
+  long long wait_acc = 0;
+  long long wait_site[LD2_NUM_BARS];
+  long long ev_sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define LD2_EV(site) ev_sum[site] += clock64();
+  for (int i = 0; i < LD2_NUM_BARS; ++i) wait_site[i] = 0;
+  auto lap_wait_timed = [&](uint32_t b, uint32_t pa, volatile int* af, long long bud) -> bool {
+    const long long t0 = clock64();
+    const bool ok = lab200::lap_wait(b, pa, af, bud);
+    wait_acc += clock64() - t0;
+    wait_site[(b - sBar) >> 4] += clock64() - t0;
+    return ok;
+  };
+#define lap_wait lap_wait_timed
+#endif
+#ifndef LD2_EV
+#define LD2_EV(site)
+#endif
 #define LD2_FAIL(code) { if (*fail_code == 0) *fail_code = (code); }
 #define LD2_STAMP(slot, it) if (p.trace != nullptr && bh == 0 && blockIdx.y == 0 && (it) < p.trace_blocks) \
     p.trace[(it) * LA_TRACE_SLOTS + (slot)] = clock64();
-#ifdef LD2_MASK_TRACE  // debugging build: only the MMA warp's block start (slot 0) and the fine stamps of one mask warp
-#define LD2_TRACE(slot, it) if ((slot) == 0) { LD2_STAMP(slot, it) }
-#define LD2_TRACE_M(slot, it) LD2_STAMP(slot, it)
-#else
 #define LD2_TRACE(slot, it) LD2_STAMP(slot, it)
-#define LD2_TRACE_M(slot, it)
-#endif
 #define LD2_WAIT(which, it, code) if (!lap_wait(bar(which, it), par(it), abort_flag, budget)) { LD2_FAIL(code) break; }
 
   if (warp == 0) {
-    // =========================================== TMA producer ===========================================
-    // Loads of block it are issued as their buffers come free during block it-1; in between, the two staged output tiles of
-    // block it-1 are stored. The order below is the order in which these events happen in a block.
-    if (lane == 0) {
-      auto store_tile = [&](int i, int u) -> bool {  // tile u (0: dk, 1: dv) of block i: staged -> global, then free the buffer
-        if (!lap_wait(bar(u ? LD2_O_STAGED1 : LD2_O_STAGED0, i), par(i), abort_flag, budget)) return false;
-        const int nslab = u ? NE : ND;
-        for (int sl = 0; sl < nslab; ++sl)
-          tma_store_3d(u ? static_cast<const void*>(&tmDV) : static_cast<const void*>(&tmDK), sO + sl * SLAB, sl * 64,
-                       blk_of(i) * LA_BLOCK, zc);
-        tma_store_commit();
-        tma_store_wait_read();
-        mbar_arrive(bar(u ? LD2_BUF_FREE1 : LD2_BUF_FREE0, i));
-        return true;
-      };
-      bool alive = true;
-      for (int it = 0; it < nb; ++it) {
-        const int blk = blk_of(it);
-        const int st = it & 1;
-        alive = false;
-#if defined(LD2_PF)
-        if (it + 1 < nb) {
-          const int nblk = blk_of(it + 1);
-          for (int sl = 0; sl < NE; ++sl) tma_prefetch_l2_3d(&tmV, sl * 64, nblk * LA_BLOCK, zc);
-          for (int sl = 0; sl < ND; ++sl) tma_prefetch_l2_3d(&tmK, sl * 64, nblk * LA_BLOCK, zc);
-#if LD2_PF >= 2
-          for (int sl = 0; sl < 2; ++sl) tma_prefetch_l2_3d(&tmQ, sl * 64, nblk * LA_BLOCK, zc);
-#endif
-        }
-#endif
-        // do: P1 do of block it-2 was the last reader of this stage
-        if (it >= 2) { LD2_WAIT(LD2_PC1_DONE, it - 2, LA_ERR_WAIT_MMA2) }
-        mbar_arrive_expect_tx(bar(LD2_FULL_G, it), NE * SLAB);
-        for (int sl = 0; sl < NE; ++sl)
-          tma_load_3d(sG + (st * 2 + sl) * SLAB, &tmG, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_G, it));
-        // v of the previous block: S0 has consumed it (P0 exists) and its scaled copy sits in TMEM
-        if (it >= 1) { LD2_WAIT(LD2_VS_READY, it - 1, LA_ERR_WAIT_MMA1) }
-        mbar_arrive_expect_tx(bar(LD2_FULL_V, it), NE * SLAB);
-        for (int sl = 0; sl < NE; ++sl) tma_load_3d(sV + sl * SLAB, &tmV, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_V, it));
-        if (it >= 1 && !store_tile(it - 1, 0)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
-        // q of the previous block: D was its last reader
-        if (it >= 1) { LD2_WAIT(LD2_D_DONE, it - 1, LA_ERR_WAIT_MMA2) }
-        mbar_arrive_expect_tx(bar(LD2_FULL_Q, it), 2 * SLAB);
+    // =========================================== TMA loads ==============================================
+    // Prologue: everything block 0 needs, do of block 1, and (once Vs of block 0 exists) v of block 1. Then, per block it,
+    // the reloads in the order in which their buffers come free: q (D has read it), k (Ks exists), do two blocks ahead
+    // (P1 do has read the stage), v two blocks ahead (Vs of the next block exists).
+    if (issuer_lane(lane)) {
+      auto load_q = [&](int i) {
+        mbar_arrive_expect_tx(bar(LD2_FULL_Q, i), 2 * SLAB);
         for (int sl = 0; sl < 2; ++sl)  // q always as two slabs: it is the M = 128 side of the state MMA
-          tma_load_3d(sQ + sl * SLAB, &tmQ, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_Q, it));
-        if (it >= 1) { LD2_WAIT(LD2_KS_READY, it - 1, LA_ERR_WAIT_MMA1) }
-        mbar_arrive_expect_tx(bar(LD2_FULL_K, it), ND * SLAB);
-        for (int sl = 0; sl < ND; ++sl) tma_load_3d(sK + sl * SLAB, &tmK, sl * 64, blk * LA_BLOCK, zc, bar(LD2_FULL_K, it));
-        if (it >= 1 && !store_tile(it - 1, 1)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
-        alive = true;
+          tma_load_3d(sQ + sl * SLAB, &tmQ, sl * 64, blk_of(i) * LA_BLOCK, zc, bar(LD2_FULL_Q, i));
+      };
+      auto load_k = [&](int i) {
+        mbar_arrive_expect_tx(bar(LD2_FULL_K, i), ND * SLAB);
+        for (int sl = 0; sl < ND; ++sl) tma_load_3d(sK + sl * SLAB, &tmK, sl * 64, blk_of(i) * LA_BLOCK, zc, bar(LD2_FULL_K, i));
+      };
+      auto load_v = [&](int i) {
+        mbar_arrive_expect_tx(bar(LD2_FULL_V, i), NE * SLAB);
+        for (int sl = 0; sl < NE; ++sl) tma_load_3d(sV + sl * SLAB, &tmV, sl * 64, blk_of(i) * LA_BLOCK, zc, bar(LD2_FULL_V, i));
+      };
+      auto load_g = [&](int i) {
+        mbar_arrive_expect_tx(bar(LD2_FULL_G, i), NE * SLAB);
+        for (int sl = 0; sl < NE; ++sl)
+          tma_load_3d(sG + ((i & 1) * 2 + sl) * SLAB, &tmG, sl * 64, blk_of(i) * LA_BLOCK, zc, bar(LD2_FULL_G, i));
+      };
+      if (nb > 0) {
+        load_v(0); load_g(0); load_k(0); load_q(0);
+        if (nb > 1) load_g(1);
       }
-      if (alive && nb > 0 && *abort_flag == 0) {
-        if (!store_tile(nb - 1, 0) || !store_tile(nb - 1, 1)) LD2_FAIL(LA_ERR_WAIT_MMA2)
+      do {
+        if (nb > 1) {
+          LD2_WAIT(LD2_PV0_READY, 0, LA_ERR_WAIT_MMA1)
+          load_v(1);
+        }
+        for (int it = 0; it < nb; ++it) {
+          if (it + 1 < nb) {
+            // q and k of the next block go to L2 now, a block before their loads: those loads sit in the chains that bound
+            // the block (D -> q -> S1, Ks -> k -> S1) and complete in ~1,300 cycles from L2 instead of ~2,800 from HBM.
+            // (Prefetching v and do as well was measured slower.)
+            for (int sl = 0; sl < 2; ++sl) tma_prefetch_l2_3d(&tmQ, sl * 64, blk_of(it + 1) * LA_BLOCK, zc);
+            for (int sl = 0; sl < ND; ++sl) tma_prefetch_l2_3d(&tmK, sl * 64, blk_of(it + 1) * LA_BLOCK, zc);
+          }
+          if (it + 1 < nb) {
+            LD2_WAIT(LD2_D_DONE, it, LA_ERR_WAIT_MMA2)
+            load_q(it + 1);
+            LD2_EV(0)
+            LD2_WAIT(LD2_PK1_READY, it, LA_ERR_WAIT_MMA1)
+            load_k(it + 1);
+            LD2_EV(1)
+          }
+          if (it + 2 < nb) {
+            LD2_WAIT(LD2_PC1_DONE, it, LA_ERR_WAIT_MMA2)
+            load_g(it + 2);
+            LD2_EV(2)
+            LD2_WAIT(LD2_PV0_READY, it + 1, LA_ERR_WAIT_MMA1)
+            load_v(it + 2);
+            LD2_EV(3)
+          }
+        }
+      } while (false);
+    }
+  } else if (warp == 14) {
+    // =========================================== TMA stores =============================================
+    // The two staged output tiles of a block leave in turn through the one staging buffer.
+    if (issuer_lane(lane)) {
+      for (int it = 0; it < nb; ++it) {
+        bool ok = true;
+#pragma unroll 1
+        for (int u = 0; u < 2 && ok; ++u) {
+          ok = lap_wait(bar(u ? LD2_O_STAGED1 : LD2_O_STAGED0, it), par(it), abort_flag, budget);
+          if (!ok) break;
+          const int nslab = u ? NE : ND;
+          for (int sl = 0; sl < nslab; ++sl)
+            tma_store_3d(u ? static_cast<const void*>(&tmDV) : static_cast<const void*>(&tmDK), sO + sl * SLAB, sl * 64,
+                         blk_of(it) * LA_BLOCK, zc);
+          tma_store_commit();
+          tma_store_wait_read();
+          mbar_arrive(bar(u ? LD2_BUF_FREE1 : LD2_BUF_FREE0, it));
+          LD2_EV(u)
+        }
+        if (!ok) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
       }
       tma_store_wait_all();
     }
   } else if (warp == 1) {
     // ============================================ MMA issuer ============================================
-    // Issue order per block: [P0 q, Vs dKV^T] -> dk; S0 of the next block; D (the last reader of q, whose buffer is then
-    // reloaded); [P1 do, Ks dKV] -> dv; S1 of the next block. The two S products of block it+1 are in TMEM before the mask
-    // group gets to them.
-    if (lane == 0) {
+    if (issuer_lane(lane)) {
       auto issue_S0 = [&](int i) -> bool {  // S0 = v do^T (contraction over e)
         if (!lap_wait(bar(LD2_FULL_V, i), par(i), abort_flag, budget)) return false;
         if (!lap_wait(bar(LD2_FULL_G, i), par(i), abort_flag, budget)) return false;
@@ -220,10 +268,9 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!lap_wait(bar(LD2_FULL_K, i), par(i), abort_flag, budget)) return false;
         if (!lap_wait(bar(LD2_FULL_Q, i), par(i), abort_flag, budget)) return false;
         tc_fence_after_sync();
-        const uint32_t q0 = sQ;
         for (int kq = 0; kq < nd16; ++kq) {
           const uint32_t off = (kq >> 2) * SLAB + (kq & 3) * 32;
-          umma_f16(tmem + T_SB, smem_desc_sw128(sK + off, 16), smem_desc_sw128(q0 + off, 16), IDESC_S, kq > 0);
+          umma_f16(tmem + T_SB, smem_desc_sw128(sK + off, 16), smem_desc_sw128(sQ + off, 16), IDESC_S, kq > 0);
         }
         umma_commit(bar(LD2_S1_READY, i));
         return true;
@@ -234,19 +281,21 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!alive) LD2_FAIL(LA_ERR_WAIT_INPUT)
       }
       for (int it = 0; it < nb && alive; ++it) {
-        const uint32_t sQs = sQ, sGs = sG + (it & 1) * 2 * SLAB;
+        const uint32_t sGs = sG + (it & 1) * 2 * SLAB;
         const bool have_state = have_state_in || (it > 0);
         LD2_TRACE(0, it)
-        // ---- dk = P0 q + Vs dKV^T -------------------------------------------------------------------------------
-        LD2_WAIT(LD2_P0_READY, it, LA_ERR_WAIT_MMA1)
+        LD2_EV(0)
+        // ---- dk = P0 q + Vs dKV^T; the first half is the last reader of the unscaled q tile ----------------------------
+        LD2_WAIT(LD2_PV0_READY, it, LA_ERR_WAIT_MMA1)
         if (it > 0) { LD2_WAIT(LD2_O_FREE1, it - 1, LA_ERR_WAIT_MMA2) }  // the dv epilogue of the previous block has read O
-        LD2_TRACE(1, it)
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_f16_ts(tmem + T_O, tmem + T_SA + kk * 8, smem_desc_sw128(sQs + kk * 2048, SLAB), IDESC_PC0, kk > 0);
+          umma_f16_ts(tmem + T_O, tmem + T_SA + kk * 8, smem_desc_sw128(sQ + kk * 2048, SLAB), IDESC_PC0, kk > 0);
+        umma_commit(bar(LD2_QP_DONE, it));
+        LD2_TRACE(1, it)
+        LD2_EV(1)
         if (have_state) {
-          LD2_WAIT(LD2_VS_READY, it, LA_ERR_WAIT_MMA2)
           LD2_WAIT(LD2_STATE_READY, it, LA_ERR_WAIT_MMA2)
           tc_fence_after_sync();
           for (int kq = 0; kq < ne16; ++kq) {  // contraction over e: state copy columns
@@ -256,21 +305,24 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         umma_commit(bar(LD2_PC0_DONE, it));
         LD2_TRACE(2, it)
+        LD2_EV(2)
         if (it + 1 < nb) {
           if (!issue_S0(it + 1)) { LD2_FAIL(LA_ERR_WAIT_INPUT) break; }
         }
         LD2_TRACE(3, it)
-        // ---- D = (w_state q)^T do ------------------------------------------------------------------------------
+        LD2_EV(3)
+        // ---- D = (w_state q)^T do: the last reader of q ------------------------------------------------------------------
         LD2_WAIT(LD2_Q_SCALED, it, LA_ERR_WAIT_MMA2)
         if (it > 0) { LD2_WAIT(LD2_D_FREE, it - 1, LA_ERR_WAIT_MMA2) }
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem + T_D, smem_desc_sw128(sQs + kk * 2048, SLAB), smem_desc_sw128(sGs + kk * 2048, SLAB), IDESC_D, kk > 0);
+          umma_f16(tmem + T_D, smem_desc_sw128(sQ + kk * 2048, SLAB), smem_desc_sw128(sGs + kk * 2048, SLAB), IDESC_D, kk > 0);
         umma_commit(bar(LD2_D_DONE, it));
         LD2_TRACE(7, it)
+        LD2_EV(4)
         // ---- dv = P1 do + Ks dKV -----------------------------------------------------------------------------------
-        LD2_WAIT(LD2_P1_READY, it, LA_ERR_WAIT_MMA1)
+        LD2_WAIT(LD2_PK1_READY, it, LA_ERR_WAIT_MMA1)
         LD2_WAIT(LD2_O_FREE0, it, LA_ERR_WAIT_MMA2)  // the dk epilogue has read O
         LD2_TRACE(4, it)
         tc_fence_after_sync();
@@ -278,23 +330,25 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int kk = 0; kk < 8; ++kk)
           umma_f16_ts(tmem + T_O, tmem + T_SB + kk * 8, smem_desc_sw128(sGs + kk * 2048, SLAB), IDESC_PC1, kk > 0);
         if (have_state) {
-          LD2_WAIT(LD2_KS_READY, it, LA_ERR_WAIT_MMA2)
-          tc_fence_after_sync();
           for (int kq = 0; kq < nd16; ++kq)  // contraction over d: state copy rows
             umma_f16_ts(tmem + T_O, tmem + T_SB + T_XA + kq * 8, smem_desc_sw128(sS + kq * 2048, SLAB), IDESC_X1, 1);
         }
         umma_commit(bar(LD2_PC1_DONE, it));
         LD2_TRACE(5, it)
+        LD2_EV(5)
         if (it + 1 < nb) {
           if (!issue_S1(it + 1)) { LD2_FAIL(LA_ERR_WAIT_INPUT) break; }
         }
         LD2_TRACE(6, it)
+        LD2_EV(6)
       }
     }
   } else if (warp < 6) {
     // ============================================ mask group ============================================
     // Reverse-time mask on both products: keep c >= r with lambda^(c-r). One warp per TMEM lane quadrant, four 32-column
     // tiles each, in column order; P tile t goes back over S columns [16 t, 16 t + 16), which the warp has read by then.
+    // Behind each pass the same warp writes the scaled copy of its 32 rows of v (k) into columns [64, 128) of the region,
+    // whose S values it has consumed: pass 1 and Ks of block it, then pass 0 and Vs of block it + 1.
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lanebase = static_cast<uint32_t>(q * 32) << 16;
@@ -305,67 +359,87 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // table is used instead for decay rates where it could leave the fp32 range (CTA-uniform choice).
     const bool diag_rank1 = s * 31.f < 60.f;
     const float rowd = diag_rank1 ? ex2f(-s2 * static_cast<float>(lane)) : 0.f;
-    bool alive = true;
-    for (int it = 0; it < nb && alive; ++it) {
+    const float w_out = ex2f(s2 * static_cast<float>(LA_BLOCK - r));  // reverse time
+    const uint32_t w_out2 = pack2<FMT>(w_out, w_out);
+
+    // one mask pass over region T_S (S product of block i) followed by the scaled copy of `tile`; arrives on `ready`
+    auto pass = [&](int u, int i) -> bool {
+      const uint32_t T_S = u ? T_SB : T_SA;
+      bool ok = lap_wait(bar(u ? LD2_S1_READY : LD2_S0_READY, i), par(i), abort_flag, budget);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return false;
+      if (q == 0 && lane == 0) { LD2_TRACE(8 + 2 * u, i) }
+      LD2_EV(2 * u)
+      tc_fence_after_sync();
 #pragma unroll 1
-      for (int u = 0; u < 2; ++u) {
-        const uint32_t T_S = u ? T_SB : T_SA;
-        bool ok = lap_wait(bar(u ? LD2_S1_READY : LD2_S0_READY, it), par(it), abort_flag, budget);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { LD2_FAIL(LA_ERR_WAIT_MMA1) alive = false; break; }
-        if (q == 0 && lane == 0) { LD2_TRACE(8 + 2 * u, it) }
-        if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(15, it) }
-        tc_fence_after_sync();
-#pragma unroll 1
-        for (int t = 0; t < 4; ++t) {
-          const int c0 = t * 32;
-          const int kind = (t == q) ? 2 : ((t > q) ? 1 : 0);  // 0 dead, 1 live, 2 diagonal; warp-uniform
-          uint32_t v[32];
-          if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(t * 3 + 1, it) }
-          if (kind) {
-            tmem_ld32(tmem + lanebase + T_S + c0, v);
-            tmem_wait_ld();
-          }
-          if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(t * 3 + 2, it) }
-          uint32_t pk[16];
-          if (kind == 1) {
-            const float rowf = decay_tab[c0 - r];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2)
-              pk[i >> 1] = pack2<FMT>(__uint_as_float(v[i]) * (rowf * g[i]), __uint_as_float(v[i + 1]) * (rowf * g[i + 1]));
-          } else if (kind == 2 && diag_rank1) {
-            // Masked elements (column i < lane) are zeroed by AND-ing the value's bits with a sign mask, not by a select on
-            // the product: the compiler turned 32 selects into 32 branches per tile, and the diagonal tile, ~150 instructions
-            // otherwise, then took ~2,800 cycles (clock stamps), which made the mask passes the bound of the whole kernel.
-            float rd = rowd;
-            asm volatile("" : "+f"(rd));  // keeps the 32 products rd * g[i] from being hoisted out of the block loop into registers
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const uint32_t k0 = ~static_cast<uint32_t>((i - lane) >> 31), k1 = ~static_cast<uint32_t>((i + 1 - lane) >> 31);
-              pk[i >> 1] = pack2<FMT>(__uint_as_float(v[i] & k0) * (rd * g[i]), __uint_as_float(v[i + 1] & k1) * (rd * g[i + 1]));
-            }
-          } else if (kind == 2) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const int d0 = i - lane, d1 = d0 + 1;
-              const uint32_t k0 = ~static_cast<uint32_t>(d0 >> 31), k1 = ~static_cast<uint32_t>(d1 >> 31);
-              const float m0 = decay_tab[max(d0, 0)], m1 = decay_tab[max(d1, 0)];
-              pk[i >> 1] = pack2<FMT>(__uint_as_float(v[i] & k0) * m0, __uint_as_float(v[i + 1] & k1) * m1);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = 0u;
-          }
-          tmem_st16(tmem + lanebase + T_S + t * 16, pk);
-          if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(t * 3 + 3, it) }
+      for (int t = 0; t < 4; ++t) {
+        const int c0 = t * 32;
+        const int kind = (t == q) ? 2 : ((t > q) ? 1 : 0);  // 0 dead, 1 live, 2 diagonal; warp-uniform
+        uint32_t v[32];
+        if (kind) {
+          tmem_ld32(tmem + lanebase + T_S + c0, v);
+          tmem_wait_ld();
         }
-        if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(13, it) }
-        tmem_wait_st();
-        if (q == 0 && lane == 0 && u == 1) { LD2_TRACE_M(14, it) }
-        tc_fence_before_sync();
-        mbar_arrive(bar(u ? LD2_P1_READY : LD2_P0_READY, it));
-        if (q == 0 && lane == 0) { LD2_TRACE(9 + 2 * u, it) }
+        uint32_t pk[16];
+        if (kind == 1) {
+          const float rowf = decay_tab[c0 - r];
+#pragma unroll
+          for (int i2 = 0; i2 < 32; i2 += 2)
+            pk[i2 >> 1] = pack2<FMT>(__uint_as_float(v[i2]) * (rowf * g[i2]), __uint_as_float(v[i2 + 1]) * (rowf * g[i2 + 1]));
+        } else if (kind == 2 && diag_rank1) {
+          // Masked elements (column i < lane) are zeroed by AND-ing the value's bits with a sign mask, not by a select on
+          // the product: the compiler turned 32 selects into 32 branches per tile, and the diagonal tile, ~150 instructions
+          // otherwise, then took ~2,800 cycles (clock stamps), which made the mask passes the bound of the whole kernel.
+          float rd = rowd;
+          asm volatile("" : "+f"(rd));  // keeps the 32 products rd * g[i] from being hoisted out of the block loop into registers
+#pragma unroll
+          for (int i2 = 0; i2 < 32; i2 += 2) {
+            const uint32_t k0 = ~static_cast<uint32_t>((i2 - lane) >> 31), k1 = ~static_cast<uint32_t>((i2 + 1 - lane) >> 31);
+            pk[i2 >> 1] = pack2<FMT>(__uint_as_float(v[i2] & k0) * (rd * g[i2]), __uint_as_float(v[i2 + 1] & k1) * (rd * g[i2 + 1]));
+          }
+        } else if (kind == 2) {
+#pragma unroll
+          for (int i2 = 0; i2 < 32; i2 += 2) {
+            const int d0 = i2 - lane, d1 = d0 + 1;
+            const uint32_t k0 = ~static_cast<uint32_t>(d0 >> 31), k1 = ~static_cast<uint32_t>(d1 >> 31);
+            const float m0 = decay_tab[max(d0, 0)], m1 = decay_tab[max(d1, 0)];
+            pk[i2 >> 1] = pack2<FMT>(__uint_as_float(v[i2] & k0) * m0, __uint_as_float(v[i2 + 1] & k1) * m1);
+          }
+        } else {
+#pragma unroll
+          for (int i2 = 0; i2 < 16; ++i2) pk[i2] = 0u;
+        }
+        tmem_st16(tmem + lanebase + T_S + t * 16, pk);
       }
+      // scaled copy: row r of the [128][64 NS] tile times w(r) -> bf16 pairs -> columns [T_S + 64, ...), 4 columns per 16-byte chunk
+      const uint32_t tile = u ? sK : sV;
+      const int nch = (u ? ND : NE) * 8;  // 16-byte chunks in the row
+#pragma unroll 1
+      for (int c4 = 0; c4 < nch; c4 += 4) {
+        uint32_t w[16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int gch = c4 + c;
+          ld_shared_v4(tile + (gch >> 3) * SLAB + r * 128 + ((((gch & 7) ^ (r & 7))) << 4), w[c * 4], w[c * 4 + 1], w[c * 4 + 2],
+                       w[c * 4 + 3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = mul2<FMT>(w[j], w_out2);
+        tmem_st16(tmem + lanebase + T_S + T_XA + c4 * 4, w);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar(u ? LD2_PK1_READY : LD2_PV0_READY, i));
+      if (q == 0 && lane == 0) { LD2_TRACE(9 + 2 * u, i) }
+      LD2_EV(2 * u + 1)
+      return true;
+    };
+    bool alive = (nb == 0) || pass(0, 0);
+    if (!alive) LD2_FAIL(LA_ERR_WAIT_MMA1)
+    for (int it = 0; it < nb && alive; ++it) {
+      alive = pass(1, it);
+      if (alive && it + 1 < nb) alive = pass(0, it + 1);
+      if (!alive) LD2_FAIL(LA_ERR_WAIT_MMA1)
     }
   } else {
     // ========================================= state / output group =====================================
@@ -373,8 +447,6 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q = warp & 3, hf = w8 >> 2;
     const int r = q * 32 + lane;
     const uint32_t lanebase = static_cast<uint32_t>(q * 32) << 16;
-    const float w_out = ex2f(s2 * static_cast<float>(LA_BLOCK - r));  // reverse time
-    const uint32_t w_out2 = pack2<FMT>(w_out, w_out);
     const float w_state = ex2f(s2 * static_cast<float>(r));
     const uint32_t w_state2 = pack2<FMT>(w_state, w_state);
     const float decay_blk = ex2f(s2 * static_cast<float>(LA_BLOCK));
@@ -409,33 +481,8 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_arrive(bar(LD2_STATE_READY, 0));  // state entering block 0
 
-    // Row r of a [128][64 NS] shared-memory tile, scaled by w(r), as the A operand of a TMEM-sourced MMA: this thread's
-    // half of the row's 16-byte chunks -> bf16 pairs -> TMEM columns [T + 4 * chunk, ...).
-    auto scaled_copy_to_tmem = [&](auto ns_tag, uint32_t tile, uint32_t tcol) {
-      constexpr int NS = decltype(ns_tag)::value;
-      constexpr int NCH = NS * 4;  // chunks per thread
-      uint32_t u[NCH][4];
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        const int gch = hf * NCH + c;  // chunk index in the row, 0 .. NS*8-1
-        ld_shared_v4(tile + (gch >> 3) * SLAB + r * 128 + ((((gch & 7) ^ (r & 7))) << 4), u[c][0], u[c][1], u[c][2], u[c][3]);
-      }
-#pragma unroll
-      for (int c4 = 0; c4 < NCH; c4 += 4) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) pk[c * 4 + j] = mul2<FMT>(u[c4 + c][j], w_out2);
-        }
-        tmem_st16(tmem + lanebase + tcol + (hf * NCH + c4) * 4, pk);
-      }
-      tmem_wait_st();
-      tc_fence_before_sync();
-    };
-
-    // epilogue of half U: O -> registers -> swizzled tile in the staging buffer (dk for U = 0, dv for U = 1); the producer
-    // warp stores it. The buffer is free once the previous tile (the other half) has been read by its TMA store.
+    // epilogue of half U: O -> registers -> swizzled tile in the staging buffer (dk for U = 0, dv for U = 1); the store
+    // warp sends it off. The buffer is free once the previous tile (the other half) has been read by its TMA store.
     auto epilogue = [&](auto u_tag, int it) -> bool {
       constexpr int U = decltype(u_tag)::value;
       constexpr int OC = (U == 0 ? DQ : DE) / 2;
@@ -471,22 +518,10 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     for (int it = 0; it < nb; ++it) {
       const bool has_next = (it + 1 < nb);
-      // ---- Vs = w v into SA[64, 128): the mask group is done with S0 ----------------------------------------------
+      // ---- q rows *= w_state(r), in place, for D: S1 and P0 q are done with the unscaled tile; first in the block because
+      //      the next load of q waits for D -----------------------------------------------------------------------------
       {
-        bool ok = lap_wait(bar(LD2_P0_READY, it), par(it), abort_flag, budget);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { LD2_FAIL(LA_ERR_WAIT_MMA1) break; }
-        tc_fence_after_sync();
-        scaled_copy_to_tmem(std::integral_constant<int, NE>{}, sV, T_SA + T_XA);
-        mbar_arrive(bar(LD2_VS_READY, it));
-        if (tracer) { LD2_TRACE(12, it) }
-      }
-      // ---- dk tile ---------------------------------------------------------------------------------------------
-      if (!epilogue(std::integral_constant<int, 0>{}, it)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
-      if (tracer) { LD2_TRACE(13, it) }
-      // ---- q rows *= w_state(r), in place, for D: S1 and P0 q are done with the unscaled tile -------------------------
-      {
-        bool ok = lap_wait(bar(LD2_S1_READY, it), par(it), abort_flag, budget);
+        bool ok = lap_wait(bar(LD2_QP_DONE, it), par(it), abort_flag, budget);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { LD2_FAIL(LA_ERR_WAIT_MMA1) break; }
         if (s != 0.f) {
@@ -510,17 +545,13 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           fence_proxy_async_smem();
         }
         mbar_arrive(bar(LD2_Q_SCALED, it));
+        if (tracer) { LD2_TRACE(12, it) }
+        LD2_EV(0)
       }
-      // ---- Ks = w k into SB[64, 128) ---------------------------------------------------------------------------------
-      {
-        bool ok = lap_wait(bar(LD2_P1_READY, it), par(it), abort_flag, budget);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { LD2_FAIL(LA_ERR_WAIT_MMA1) break; }
-        tc_fence_after_sync();
-        scaled_copy_to_tmem(std::integral_constant<int, ND>{}, sK, T_SB + T_XA);
-        mbar_arrive(bar(LD2_KS_READY, it));
-        if (tracer) { LD2_TRACE(14, it) }
-      }
+      // ---- dk tile ---------------------------------------------------------------------------------------------
+      if (!epilogue(std::integral_constant<int, 0>{}, it)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
+      if (tracer) { LD2_TRACE(13, it) }
+      LD2_EV(1)
       // ---- state recurrence: dKV = lambda^128 dKV + D (registers; the shared-memory copy follows the dv half) ---------
       {
         bool ok = lap_wait(bar(LD2_D_DONE, it), par(it), abort_flag, budget);
@@ -538,14 +569,18 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_before_sync();
       mbar_arrive(bar(LD2_D_FREE, it));
+      if (tracer) { LD2_TRACE(14, it) }
+      LD2_EV(2)
       // ---- dv tile ---------------------------------------------------------------------------------------------
       if (!epilogue(std::integral_constant<int, 1>{}, it)) { LD2_FAIL(LA_ERR_WAIT_MMA2) break; }
+      LD2_EV(3)
       if (has_next) {  // PC1_DONE (awaited by the dv epilogue) covers both halves of this block: they are done with the old copy
         store_state_smem();
         fence_proxy_async_smem();
         mbar_arrive(bar(LD2_STATE_READY, it + 1));
       }
       if (tracer) { LD2_TRACE(15, it) }
+      LD2_EV(4)
     }
     if (*abort_flag == 0 && p.state_out != nullptr && st_row_valid) {
       float* dst = p.state_out + ((static_cast<size_t>(bh) * p.state_slots + chunk) * p.d + r) * p.e + hf * SC;
@@ -555,9 +590,18 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   }
+#ifdef LD2_WAITACC
+#undef lap_wait
+  if (p.trace != nullptr && bh == 0 && blockIdx.y == 0 && lane == 0)
+    p.trace[p.trace_blocks * LA_TRACE_SLOTS + warp] = wait_acc;
+  if (p.trace != nullptr && bh == 0 && blockIdx.y == 0 && lane == 0)
+    for (int i = 0; i < LD2_NUM_BARS; ++i) p.trace[p.trace_blocks * LA_TRACE_SLOTS + 16 + warp * LD2_NUM_BARS + i] = wait_site[i];
+  if (p.trace != nullptr && bh == 0 && blockIdx.y == 0 && lane == 0)
+    for (int i = 0; i < 8; ++i) p.trace[p.trace_blocks * LA_TRACE_SLOTS + 16 + 15 * LD2_NUM_BARS + warp * 8 + i] = ev_sum[i];
+#undef LD2_EV
+#endif
 #undef LD2_WAIT
 #undef LD2_TRACE
-#undef LD2_TRACE_M
 #undef LD2_STAMP
 #undef LD2_FAIL
 

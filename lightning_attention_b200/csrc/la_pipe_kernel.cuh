@@ -39,13 +39,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 
 // TMA store of one [128 rows][64 columns] slab, shared -> global; rows/columns outside the tensor are dropped.
 __device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int x, int y, int z) {
-#if (LA_HINT & 2)
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;"
-               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y), "r"(z), "l"(l2_policy_evict_first()) : "memory");
-#else
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
-#endif
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
@@ -151,7 +146,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // =========================================== TMA producer ===========================================
     // Also issues the TMA stores of the output tiles: a tile is staged in the A stage of its block (S and X are done
     // with A by the time P C has run), and that stage is reloaded (for block it+2) only after the store has read it.
-    if (lane == 0) {
+    if (issuer_lane(lane)) {
       auto blk_of = [&](int i) { return reverse ? (blk_end - 1 - i) : (blk_begin + i); };
       auto store_tile = [&](int i) -> bool {  // output tile of block i: wait until it is staged, then store it
         const int sst = i & 1;
@@ -205,7 +200,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // S_{i+1} overwrites the TMEM columns P_i lives in, so it follows PC_i (the tensor pipe executes in issue order).
     // D and P C commit to their own barriers: the state update starts after D_i, the output tile leaves TMEM after
     // PC_i while S_{i+1}, X_{i+1} and D_{i+1} run.
-    if (lane == 0) {
+    if (issuer_lane(lane)) {
       auto issue_S = [&](int i) -> bool {
         const int ist = i & 1;
         if (!lap_wait(bar(LAP_FULL_A, ist), (i >> 1) & 1, abort_flag, budget)) return false;
