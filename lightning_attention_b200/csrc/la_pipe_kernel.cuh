@@ -24,7 +24,7 @@ constexpr int LAP_MASK_THREADS = 128, LAP_STATE_THREADS = 256;
 
 
 // barrier slots (each has two instances, indexed by block parity)
-enum : int { LAP_FULL_A = 0, LAP_FULL_BC, LAP_S_READY, LAP_P_READY, LAP_PC_DONE, LAP_D_DONE, LAP_O_FREE, LAP_D_FREE,
+enum : int { LAP_FULL_AB = 0, LAP_FULL_C, LAP_S_READY, LAP_P_READY, LAP_PC_DONE, LAP_D_DONE, LAP_O_FREE, LAP_D_FREE,
              LAP_STATE_READY, LAP_O_STAGED, LAP_BM_SCALED, LAP_NUM_BARS };
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -85,7 +85,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t sB = sA + (MODE == 0 ? 2 * NAS * SLAB : 0);        // 2 stages x NKS slabs
   const uint32_t sC = sB + 2 * NKS * SLAB;                          // 2 stages x 2 slabs
   const uint32_t sS = sC + 2 * 2 * SLAB;                            // bf16 state, NKS x [DV rows][128 B] (MODE 0)
-  // Output tiles are staged in the A stage of their own block (free once S and X are done) and leave by TMA store.
+  // Output tiles are staged in the C stage of their own block (free once P C is done) and leave by TMA store.
   const uint32_t sBar = sS + (MODE == 0 ? NKS * DV * 128 : 0);      // 2 x LAP_NUM_BARS mbarriers
   const uint32_t sMisc = sBar + 2 * LAP_NUM_BARS * 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sMisc - raw));
@@ -144,8 +144,8 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     // =========================================== TMA producer ===========================================
-    // Also issues the TMA stores of the output tiles: a tile is staged in the A stage of its block (S and X are done
-    // with A by the time P C has run), and that stage is reloaded (for block it+2) only after the store has read it.
+    // Also issues the TMA stores of the output tiles: a tile is staged in the C stage of its block (P C, the last MMA of a
+    // block, has read C by then), and that stage is reloaded (for block it+2) only after the store has read it.
     if (issuer_lane(lane)) {
       auto blk_of = [&](int i) { return reverse ? (blk_end - 1 - i) : (blk_begin + i); };
       auto store_tile = [&](int i) -> bool {  // output tile of block i: wait until it is staged, then store it
@@ -153,7 +153,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!lap_wait(bar(LAP_O_STAGED, sst), (i >> 1) & 1, abort_flag, budget)) return false;
 #pragma unroll
         for (int vs = 0; vs < NVS; ++vs)
-          tma_store_3d(&tmO, sA + (sst * NAS + vs) * SLAB, dv_off + vs * 64, blk_of(i) * LA_BLOCK, zc);
+          tma_store_3d(&tmO, sC + (sst * 2 + vs) * SLAB, dv_off + vs * 64, blk_of(i) * LA_BLOCK, zc);
         tma_store_commit();
         return true;
       };
@@ -162,29 +162,30 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int blk = blk_of(it);
         const int st = it & 1;
         const uint32_t prev_par = ((it >> 1) & 1) ^ 1;  // parity of the previous use of this stage (block it-2)
-        if (MODE == 0) {
-          if (it >= 2) {
-            // A staged output tile means P C of block it-2 has run, the last MMA to touch that block's A, Bm and C.
-            // The A stage holds the tile: store it; Bm and C can be reloaded at once, A when the store has read the tile.
-            if (!store_tile(it - 2)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
-          }
-        } else if (it >= 2) {
-          if (!lap_wait(bar(LAP_D_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
+        // A and Bm of block it: their stages are free once every MMA of block it-2 has run (P C is the last one issued; in
+        // state-only mode D). They are what S of block it waits for, so they go first and wait for nothing else.
+        if (it >= 2) {
+          if (!lap_wait(bar(MODE == 0 ? LAP_PC_DONE : LAP_D_DONE, st), prev_par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         }
-        mbar_arrive_expect_tx(bar(LAP_FULL_BC, st), (NKS + 2) * SLAB);
+        mbar_arrive_expect_tx(bar(LAP_FULL_AB, st), (MODE == 0 ? 2 * NKS : NKS) * SLAB);
 #pragma unroll
         for (int ks = 0; ks < NKS; ++ks)
-          tma_load_3d(sB + (st * NKS + ks) * SLAB, &tmB, ks * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_BC, st));
-#pragma unroll
-        for (int vs = 0; vs < 2; ++vs)
-          tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_BC, st));
+          tma_load_3d(sB + (st * NKS + ks) * SLAB, &tmB, ks * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_AB, st));
         if (MODE == 0) {
-          if (it >= 2) tma_store_wait_read();
-          mbar_arrive_expect_tx(bar(LAP_FULL_A, st), NKS * SLAB);
 #pragma unroll
           for (int ks = 0; ks < NKS; ++ks)
-            tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_A, st));
+            tma_load_3d(sA + (st * NAS + ks) * SLAB, &tmA, ks * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_AB, st));
         }
+        // C of block it: in the full block loop its stage holds the staged output tile of block it-2, which is stored first;
+        // C is not needed before D of block it, a whole block later than A and Bm.
+        if (MODE == 0 && it >= 2) {
+          if (!store_tile(it - 2)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
+          tma_store_wait_read();
+        }
+        mbar_arrive_expect_tx(bar(LAP_FULL_C, st), 2 * SLAB);
+#pragma unroll
+        for (int vs = 0; vs < 2; ++vs)
+          tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_C, st));
       }
       if (MODE == 0 && alive && *abort_flag == 0) {
         for (int i = max(nb - 2, 0); i < nb; ++i) {
@@ -203,8 +204,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (issuer_lane(lane)) {
       auto issue_S = [&](int i) -> bool {
         const int ist = i & 1;
-        if (!lap_wait(bar(LAP_FULL_A, ist), (i >> 1) & 1, abort_flag, budget)) return false;
-        if (!lap_wait(bar(LAP_FULL_BC, ist), (i >> 1) & 1, abort_flag, budget)) return false;
+        if (!lap_wait(bar(LAP_FULL_AB, ist), (i >> 1) & 1, abort_flag, budget)) return false;
         tc_fence_after_sync();
         const uint32_t a0 = sA + ist * NAS * SLAB, b0 = sB + ist * NKS * SLAB;
         for (int kq = 0; kq < nk16; ++kq) {  // S = A Bm^T
@@ -240,7 +240,8 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           LAP_TRACE(1, it)
         }
-        if (MODE != 0 && !lap_wait(bar(LAP_FULL_BC, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
+        if (MODE != 0 && !lap_wait(bar(LAP_FULL_AB, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
+        if (!lap_wait(bar(LAP_FULL_C, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_INPUT) break; }
         if (!lap_wait(bar(LAP_BM_SCALED, st), par, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         if (it > 0 && !lap_wait(bar(LAP_D_FREE, pst), ppar, abort_flag, budget)) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         tc_fence_after_sync();
@@ -397,7 +398,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     auto scale_bm = [&](int j) -> bool {
       const int st = j & 1;
       // S_j must be done with the unscaled tile (state-only mode: the tile must have landed)
-      bool ok = lap_wait(bar(MODE == 0 ? LAP_S_READY : LAP_FULL_BC, st), (j >> 1) & 1, abort_flag, budget);
+      bool ok = lap_wait(bar(MODE == 0 ? LAP_S_READY : LAP_FULL_AB, st), (j >> 1) & 1, abort_flag, budget);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) return false;
       if (s != 0.f) {
@@ -475,7 +476,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!ok) { LAP_FAIL(LA_ERR_WAIT_MMA2) break; }
         if (store_thread) { LAP_TRACE(7, it) }
         tc_fence_after_sync();
-        const uint32_t sOs = sA + st * NAS * SLAB;  // S_it and X_it are done with this A stage
+        const uint32_t sOs = sC + st * 2 * SLAB;  // P C and D of this block are done with this C stage
 #pragma unroll
         for (int cc = 0; cc < OC; cc += 16) {
           uint32_t a[16], b[16];
