@@ -318,7 +318,15 @@ int la_generic_impl(const void* a, const void* bm, const void* c, const float* s
   p.state_in = nullptr;
   p.state_out = states;
   p.chunk0 = (skip_last && reverse) ? 1 : 0;
-  if ((rc = launch_la(1, dtype, t, tB, tB, tC, tC, p, nchunks - skip_last, bh, st)) != LAB200_OK) return rc;
+  // The state-only pass runs one CTA per (dv slice, chunk that feeds a later one, pair): with two chunks per pair that is half as
+  // many CTAs as the block loop gets. When twice as many still fit in one wave, it runs on 64-wide dv slices instead of 128-wide
+  // ones (the states land in the same [dv][dk] layout; Bm is then read twice, the second time from L2).
+  Tiling ts = t;
+  if (t.nvs == 2 && 2LL * t.nslices * (nchunks - skip_last) * bh <= sm_count()) {
+    ts.nvs = 1;
+    ts.nslices = (dv + 63) / 64;
+  }
+  if ((rc = launch_la(1, dtype, ts, tB, tB, tC, tC, p, nchunks - skip_last, bh, st)) != LAB200_OK) return rc;
 
   const int elems = dv * dk;
   const long long total = static_cast<long long>(bh) * elems;

@@ -182,9 +182,11 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!store_tile(it - 2)) { LAP_FAIL(LA_ERR_WAIT_MMA2) alive = false; break; }
           tma_store_wait_read();
         }
-        mbar_arrive_expect_tx(bar(LAP_FULL_C, st), 2 * SLAB);
+        // Only the slabs of this CTA's dv slice are loaded. D = C^T (w Bm) is an M = 128 MMA and reads both slabs of the stage; with
+        // a 64-wide slice the second one holds stale bytes, which only reach accumulator rows >= 64 that nobody reads.
+        mbar_arrive_expect_tx(bar(LAP_FULL_C, st), NVS * SLAB);
 #pragma unroll
-        for (int vs = 0; vs < 2; ++vs)
+        for (int vs = 0; vs < NVS; ++vs)
           tma_load_3d(sC + (st * 2 + vs) * SLAB, &tmC, dv_off + vs * 64, blk * LA_BLOCK, zc, bar(LAP_FULL_C, st));
       }
       if (MODE == 0 && alive && *abort_flag == 0) {
