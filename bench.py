@@ -944,8 +944,18 @@ def main():
                 o_.transpose(1, 2).contiguous().backward(xdo)
 
             res = {name + "_ms": event_time(torch, fn, 5, warm=2) for name, fn in (("in_place", in_place), ("with_copies", with_copies))}
+
+            # The caller's SiLU on q, k, v (tnl_attn.py:52-54) as what it costs when it is NOT folded into the projection GEMMs'
+            # epilogue: three element-wise passes in the forward direction (read + write of each tensor).
+            def silu_prepass():
+                with torch.no_grad():
+                    for t_ in (xq, xk, xv):
+                        torch.nn.functional.silu(t_)
+
+            res["silu_prepass_fwd_ms"] = event_time(torch, silu_prepass, 5, warm=2)
             proj = {"shape_b_n_h_d": [B, N_TOK, H, D], **res,
-                    "note": "fwd+bwd with q, k, v, do given as (b, n, h, d) tensors; tnl_attn.py:56-64 style caller"}
+                    "note": "fwd+bwd with q, k, v, do given as (b, n, h, d) tensors; tnl_attn.py:56-64 style caller; silu_prepass = "
+                            "torch SiLU over q, k, v as separate element-wise kernels (forward direction only)"}
             del xq, xk, xv, xdo
         except Exception as ex:
             proj = {"error": repr(ex)[:200]}

@@ -296,7 +296,7 @@ def test_sequence_parallel_math_on_one_gpu(cuda_lib, scale):
 @pytest.mark.parametrize("chunks", [1, 3])
 @pytest.mark.parametrize("b,h,n,d,e,decay", [(2, 4, 1024, 128, 128, True), (1, 3, 513, 128, 64, True), (2, 2, 300, 64, 128, True),
                                              (1, 2, 77, 32, 16, True), (1, 4, 2048, 128, 128, False), (1, 2, 128, 16, 16, True),
-                                             (1, 2, 640, 96, 112, True)])
+                                             (1, 2, 640, 96, 112, True), (1, 2, 256, 64, 64, True), (1, 1, 384, 128, 128, True)])
 def test_fused_dk_dv_sweep(cuda_lib, b, h, n, d, e, decay, chunks):
     """lab200_la2_dkdv (dk and dv in one reverse sweep, one chunk or several) through the C ABI against the fp32 reference
     gradients and against the dk, dv of two launches of the generic kernel."""
