@@ -432,7 +432,7 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // Order of work per block it: state update (after D_it), output tile (after PC_it), Bm scaling for block it+1
     // (after S_{it+1}) - the order in which the MMA warp completes them.
     bool live = true;
-    if (MODE == 0 && nb > 0) {
+    if (nb > 0) {
       live = scale_bm(0);
       if (!live) LAP_FAIL(LA_ERR_WAIT_MMA1)
     }
@@ -441,7 +441,8 @@ la_pipe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t par = (it >> 1) & 1;
       const bool has_next = (it + 1 < nb);
       const bool have_state = have_state_in || (it > 0);
-      if (MODE != 0 && !scale_bm(it)) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
+      // state-only mode: the next block's Bm tile is scaled while D of this block runs
+      if (MODE != 0 && has_next && !scale_bm(it + 1)) { LAP_FAIL(LA_ERR_WAIT_MMA1) break; }
       {
         bool ok = lap_wait(bar(LAP_D_DONE, st), par, abort_flag, budget);
         ok = __all_sync(0xffffffffu, ok);
