@@ -142,7 +142,12 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
-#ifdef LD2_WAITACC  // debugging build: every thread sums the cycles it spends inside bounded waits
+#ifdef LD2_WAITACC
+  // Debugging build (-DLD2_WAITACC), used with lab200_la_debug_trace: lane 0 of every warp of CTA (0, 0, 0) sums the cycles it
+  // spends inside bounded waits, per barrier, and the clock at a few events per block, and writes the sums behind the per-block
+  // stamps: trace[blocks * LA_TRACE_SLOTS + 16 + warp * LD2_NUM_BARS + barrier] and, after those 15 rows, [warp * 8 + event].
+  // The trace buffer must have room for them. Dividing by the block count gives the average wait per block and, relative to
+  // the MMA warp's event 0, the average time of each event inside a block.
   long long wait_acc = 0;
   long long wait_site[LD2_NUM_BARS];
   long long ev_sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
