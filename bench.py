@@ -526,17 +526,20 @@ def leg_bh_strong(torch, dist, la, dev, rank, world, q, k, v, do, s, t1_ms):
         la.lightning_attn2(q_l, k_l, v_l, s_l).backward(do_l)
 
     ms = event_time(torch, step, 20)
-    # share of the chunk-mode overhead: the two state-only passes (k, v) and (do, q) with their scans
-    st_ms = event_time(torch, lambda: (la_generic(None, k_l.detach(), v_l.detach(), s_l, state_only=True),
-                                       la_generic(None, do_l, q_l.detach(), s_l, reverse=True, state_only=True)), 10)
+    from lightning_attention_b200 import _lib
+    with torch.cuda.device(dev):
+        chunks = _lib.lib().lab200_la_plan_chunks(q_l.shape[1], N_TOK, D, D)
+    # share of the chunk-mode overhead: the two state-only passes (k, v) and (do, q) with their scans. With one chunk per pair
+    # (enough pairs to fill the GPU, e.g. the whole problem on one rank) the step runs no such pass.
+    st_ms = 0.0
+    if chunks > 1:
+        st_ms = event_time(torch, lambda: (la_generic(None, k_l.detach(), v_l.detach(), s_l, state_only=True),
+                                           la_generic(None, do_l, q_l.detach(), s_l, reverse=True, state_only=True)), 10)
     t = torch.tensor([ms, st_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, st_ms = float(t[0]), float(t[1])
     pairs = q_l.shape[1]
-    from lightning_attention_b200 import _lib
-    with torch.cuda.device(dev):
-        chunks = _lib.lib().lab200_la_plan_chunks(pairs, N_TOK, D, D)
     return {"pairs_per_gpu": pairs, "chunks_per_pair": chunks, "ms_per_step": ms, "tokens_per_s": B * N_TOK / (ms * 1e-3),
             "t1_ms": t1_ms, "efficiency": t1_ms / (world * ms), "state_passes_ms": st_ms, "state_passes_share": st_ms / ms,
             "note": "fixed total work b4 h32 n32768 split over the ranks; efficiency = T_1 / (N T_N) with T_1 = this run's "

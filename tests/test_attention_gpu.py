@@ -322,6 +322,26 @@ def test_fused_dk_dv_sweep(cuda_lib, b, h, n, d, e, decay, chunks):
     assert_parity(dv, gdv.float(), "fused-vs-generic:dv", False)
 
 
+@pytest.mark.parametrize("b,h,n", [(2, 8, 4096), (4, 32, 1024)])  # few pairs: sequences cut into chunks; 128 pairs: one sweep per pair
+def test_block_kernels_are_deterministic(cuda_lib, b, h, n):
+    """Five runs of forward + backward on the same inputs give bit-identical o, dq, dk, dv: the hand-overs between the roles of
+    the block kernels (mbarriers, TMEM and shared-memory reuse) leave no window in which a tile is read early or late."""
+    q, k, v, do = make_inputs(b, h, n, 128, 128, torch.bfloat16, 1.0)
+    s = la._build_slope_tensor(h).to(DEV)
+    ref = None
+    for _ in range(5):
+        qq, kk, vv = (t.detach().clone().requires_grad_() for t in (q, k, v))
+        o = la.lightning_attn2(qq, kk, vv, s)
+        o.backward(do)
+        torch.cuda.synchronize()
+        got = tuple(t.detach().view(torch.int16).clone() for t in (o, qq.grad, kk.grad, vv.grad))
+        if ref is None:
+            ref = got
+        else:
+            for a, b_, name in zip(got, ref, ("o", "dq", "dk", "dv")):
+                assert torch.equal(a, b_), f"{name} differs between runs"
+
+
 @pytest.mark.parametrize("chunks", [1, 2])
 @pytest.mark.parametrize("scale", [1.0, 1e-2])
 def test_fused_dk_dv_with_incoming_state_and_kept_chunk_states(cuda_lib, chunks, scale):
