@@ -278,11 +278,18 @@ TRACE_SLOTS = ["mma: block start", "mma: X issued", "mma: P and C ready", "mma: 
                "state: output tile staged"]
 
 
+DKDV_TRACE_SLOTS = ["mma: block start", "mma: P0 q issued", "mma: Vs dKV^T issued (dk half complete)", "mma: S0 of the next block issued",
+                    "mma: P1, Ks and free accumulator seen", "mma: P1 do + Ks dKV issued (dv half complete)", "mma: S1 of the next block issued",
+                    "mma: D issued", "mask: S0 ready (pass 0 runs a block ahead)", "mask: P0 and Vs written",
+                    "mask: S1 ready", "mask: P1 and Ks written", "state: q scaled", "state: dk tile staged", "state: D drained",
+                    "state: dv tile staged, state copy written"]
+
+
 def run_trace(emit):
     """In-kernel clock trace of the attention block kernel (lab200_la_debug_trace): one forward-time and one reverse-time
     launch at b4 h32 d=e=128, n = --n; CTA (0,0,0) stamps clock64() at twelve hand-over points of every 128-token block.
     Prints one JSON line per direction: the block period and each point's mean offset from the MMA warp's block start,
-    in SM cycles, over the steady-state blocks."""
+    in SM cycles, over the steady-state blocks; then the same for the fused dk + dv sweep (sixteen points)."""
     import torch
 
     import lightning_attention_b200 as la
@@ -314,6 +321,24 @@ def run_trace(emit):
         emit(json.dumps({"trace": "la_pipe_kernel", "direction": "reverse-time" if reverse else "forward-time",
                          "shape": [B, H, N_TOK, D], "blocks_averaged": hi - lo, "block_period_cycles": round(period),
                          "offsets_cycles": {name: round(x) for name, x in zip(TRACE_SLOTS, rel)}}))
+    # the fused dk + dv sweep: sixteen hand-over points per block, stamped by the MMA thread, the mask warp of the lane quadrant
+    # with the most unmasked tiles and one state/output warp
+    do = torch.randn((B, H, N_TOK, D), device=dev, generator=g).to(torch.bfloat16)
+    for _ in range(3):
+        la.la_dkdv(a, bm, c, s, do, chunks=1)
+    torch.cuda.synchronize()
+    tr = torch.zeros(nb * 16, dtype=torch.int64, device=dev)
+    L.lab200_la_debug_trace(tr.data_ptr(), nb)
+    la.la_dkdv(a, bm, c, s, do, chunks=1)
+    torch.cuda.synchronize()
+    L.lab200_la_debug_trace(None, 0)
+    t = tr.view(nb, 16).cpu()
+    lo, hi = min(8, nb // 2), max(nb - 2, nb // 2 + 1)
+    rel = (t - t[:, 0:1])[lo:hi].double().mean(0).tolist()
+    period = (t[1:, 0] - t[:-1, 0])[lo:hi].double().mean().item()
+    emit(json.dumps({"trace": "la_dkdv2_kernel", "direction": "reverse-time", "shape": [B, H, N_TOK, D], "blocks_averaged": hi - lo,
+                     "block_period_cycles": round(period), "mmas_per_block": 56,
+                     "offsets_cycles": {name: round(x) for name, x in zip(DKDV_TRACE_SLOTS, rel)}}))
 
 
 

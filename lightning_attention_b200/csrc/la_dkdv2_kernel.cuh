@@ -420,17 +420,18 @@ la_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t tile = u ? sK : sV;
       const int nch = (u ? ND : NE) * 8;  // 16-byte chunks in the row
 #pragma unroll 1
-      for (int c4 = 0; c4 < nch; c4 += 4) {
-        uint32_t w[16];
+      for (int c8 = 0; c8 < nch; c8 += 8) {  // one 64-feature slab of the row per step: eight loads in flight
+        uint32_t w[2][16];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int gch = c4 + c;
-          ld_shared_v4(tile + (gch >> 3) * SLAB + r * 128 + ((((gch & 7) ^ (r & 7))) << 4), w[c * 4], w[c * 4 + 1], w[c * 4 + 2],
-                       w[c * 4 + 3]);
+        for (int c = 0; c < 8; ++c)
+          ld_shared_v4(tile + (c8 >> 3) * SLAB + r * 128 + (((c ^ (r & 7))) << 4), w[c >> 2][(c & 3) * 4], w[c >> 2][(c & 3) * 4 + 1],
+                       w[c >> 2][(c & 3) * 4 + 2], w[c >> 2][(c & 3) * 4 + 3]);
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) w[hh][j] = mul2<FMT>(w[hh][j], w_out2);
+          tmem_st16(tmem + lanebase + T_S + T_XA + (c8 + hh * 4) * 4, w[hh]);
         }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) w[j] = mul2<FMT>(w[j], w_out2);
-        tmem_st16(tmem + lanebase + T_S + T_XA + c4 * 4, w);
       }
       tmem_wait_st();
       tc_fence_before_sync();
